@@ -1,0 +1,488 @@
+#!/usr/bin/env python
+"""Benchmark of the trident_b200 hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl reference]
+
+One "step" is one forward + backward pass of a workload (a BASELINE configuration) over one
+batch of seeded synthetic input through the public functional API. Rank 0 prints ONE JSON
+line. With N > 1 (launched by torch.distributed.run, one rank per GPU) every rank runs its
+own shard of the workload; nothing is exchanged between ranks except the barrier and the
+max-over-ranks of the device time.
+
+  value     whole-job throughput with inputs resident in HBM; the step is replayed from a
+            CUDA graph captured through the public API, timed with CUDA events
+  e2e       the same metric through the public API with HOST (pinned) buffers: host->device
+            copies of every input and device->host copies of every result inside the timed
+            region
+  roofline  the dominant kernel alone, timed with CUDA events inside this run
+  cpu_baseline  the torch eager CPU oracle on a bounded sample of the same workload
+
+`--impl reference` times the reference's CPU implementation of the path: the torch eager
+callables its tests use as oracle (the reference itself has no CPU kernels and its Triton
+kernels do not import under the installed Triton), on all host cores.
+"""
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+DEFAULT_WORKLOAD = "softmax"
+L2_BYTES = 126 * 1024 * 1024
+
+# Bounded CPU samples: keyword arguments of Workload.make that shrink the sharded dimension.
+CPU_SAMPLE = {
+    "layer_norm": ({}, "full configuration"),
+    "softmax": ({"scale": 4}, "4096 of 16384 rows"),
+    "masked_softmax": ({"scale": 4}, "4096 of 16384 rows"),
+    "rms_norm": ({"scale": 4}, "2048 of 8192 rows"),
+    "geglu": ({"scale": 32}, "256 of 8192 rows, full weight"),
+    "attention_causal": ({"scale": 16}, "8 of 128 (batch, head) slices"),
+    "attention_masked": ({"scale": 16, "_world": 8}, "1 of 128 (batch, head) slices, one mask slab"),
+}
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return {"hbm_gbs": p["hbm_gbs"], "bf16_tflops": p["bf16_tflops"],
+                "bf16_tflops_sustained": p.get("bf16_tflops_sustained", p["bf16_tflops"]), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+def unit_of(wl):
+    return "GB/s" if wl.bound == "hbm" else "TFLOP/s"
+
+
+def rate(wl, work, seconds):
+    return work / seconds / (1e9 if wl.bound == "hbm" else 1e12)
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.rows, self.proc, self.thread = index, [], None, None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+            return
+        self.thread = threading.Thread(target=self._read, daemon=True)
+        self.thread.start()
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            if len(r) < 6:
+                continue
+            try:
+                sm.append(float(r[0]))
+                mx.append(float(r[1]))
+            except ValueError:
+                continue
+            for n, v in zip(names, r[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def dist_env():
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    return rank, local, world
+
+
+def reduce_max(value, world, device):
+    if world == 1:
+        return value
+    import torch.distributed as dist
+
+    t = torch.tensor([value], dtype=torch.float64, device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def reduce_sum(value, world, device):
+    if world == 1:
+        return value
+    import torch.distributed as dist
+
+    t = torch.tensor([value], dtype=torch.float64, device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.SUM)
+    return float(t.item())
+
+
+def barrier(world):
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.barrier()
+
+
+def clone_set(tensors):
+    return {k: v.clone() for k, v in tensors.items()}
+
+
+def set_bytes(wl, tensors):
+    return sum(tensors[k].numel() * tensors[k].element_size() for k in wl.input_keys if k in tensors)
+
+
+def launches_of_one_step(wl, tensors):
+    """Kernels the library launches for one forward + backward step (its own counter)."""
+    from trident_b200 import _lib
+
+    before = _lib.total_launches()
+    wl.step(tensors)
+    torch.cuda.synchronize()
+    return _lib.total_launches() - before
+
+
+def time_device(wl, sets, steps, warmup, world, device):
+    """Device time of `steps` steps (graph replays rotating over the input sets)."""
+    for i in range(max(warmup, 3)):
+        wl.step(sets[i % len(sets)])
+    torch.cuda.synchronize()
+    graphs, mode = [], "cuda_graph"
+    try:
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for s in sets:
+                wl.step(s)
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        for s in sets:
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                keep = wl.step(s)
+            graphs.append((g, keep))
+        for g, _ in graphs:
+            g.replay()
+        torch.cuda.synchronize()
+    except Exception as exc:  # capture is an optimisation of the launch path, not of the kernels
+        sys.stderr.write(f"[bench] CUDA graph capture failed ({exc!r}); timing eager launches\n")
+        graphs, mode = [], "eager"
+        torch.cuda.synchronize()
+
+    def one(i):
+        if graphs:
+            graphs[i % len(graphs)][0].replay()
+        else:
+            wl.step(sets[i % len(sets)])
+
+    for i in range(max(warmup, 3)):
+        one(i)
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    barrier(world)
+    start.record()
+    for i in range(steps):
+        one(i)
+    stop.record()
+    torch.cuda.synchronize()
+    barrier(world)
+    ms = start.elapsed_time(stop)
+    return reduce_max(ms, world, device) / 1e3, mode
+
+
+def time_e2e(wl, tensors, steps, warmup, world, device):
+    """Public API with host buffers: H2D of every input, the step, D2H of every result."""
+    host_in = {k: v.cpu().pin_memory() for k, v in tensors.items()}
+    dev_in = {k: torch.empty_like(v, device=device) for k, v in host_in.items()}
+    first = wl.step(tensors)
+    host_out = {k: torch.empty_like(v, device="cpu").pin_memory() for k, v in first.items()}
+    h2d = sum(v.numel() * v.element_size() for v in host_in.values())
+    d2h = sum(v.numel() * v.element_size() for v in host_out.values())
+
+    def one():
+        for k, v in host_in.items():
+            dev_in[k].copy_(v, non_blocking=True)
+        res = wl.step(dev_in)
+        for k, v in res.items():
+            host_out[k].copy_(v, non_blocking=True)
+
+    for _ in range(max(warmup, 3)):
+        one()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    barrier(world)
+    start.record()
+    for _ in range(steps):
+        one()
+    stop.record()
+    torch.cuda.synchronize()
+    barrier(world)
+    return reduce_max(start.elapsed_time(stop), world, device) / 1e3, h2d, d2h
+
+
+def dominant_kernel(wl, tensors):
+    """(label, launch closure, algorithmic work per launch) of the workload's dominant kernel,
+    called directly through the ctypes binding of the C ABI."""
+    from trident_b200 import _lib
+
+    dev = tensors[wl.input_keys[0]].device
+    if wl.name in ("softmax", "masked_softmax"):
+        x, dy = tensors["x"], tensors["dy"]
+        y, dx = torch.empty_like(x), torch.empty_like(x)
+        _lib.softmax_fwd(y, x, None, x.shape[0], x.shape[1], x.stride(0), 1)
+        return ("softmax_bwd_vec", lambda: _lib.softmax_bwd(dx, dy, y, x.shape[0], x.shape[1], x.stride(0), 1),
+                3.0 * x.numel() * x.element_size())
+    if wl.name == "layer_norm":
+        x, dy, w = tensors["x"], tensors["dy"], tensors["w"]
+        rows, cols = x.shape
+        y, dx = torch.empty_like(x), torch.empty_like(x)
+        mean = torch.empty(rows, device=dev)
+        rstd = torch.empty(rows, device=dev)
+        dw, db = torch.empty_like(w), torch.empty_like(w)
+        ws = torch.empty(_lib.layer_norm_bwd_workspace(rows, cols), dtype=torch.uint8, device=dev)
+        _lib.layer_norm_fwd(y, mean, rstd, x, w, tensors["b"], rows, cols, 1e-5)
+        return ("ln_bwd_vec(+finalize)",
+                lambda: _lib.layer_norm_bwd(dx, dw, db, dy, x, w, mean, rstd, ws, rows, cols),
+                3.0 * x.numel() * x.element_size())
+    if wl.name == "rms_norm":
+        x, dy, w = tensors["x"], tensors["dy"], tensors["w"]
+        rows, cols = x.shape
+        y, dx = torch.empty_like(x), torch.empty_like(x)
+        rms = torch.empty(rows, device=dev)
+        dw = torch.empty_like(w)
+        ws = torch.empty(_lib.rms_norm_bwd_workspace(rows, cols), dtype=torch.uint8, device=dev)
+        _lib.rms_norm_fwd(y, rms, x, w, None, rows, cols, cols, 1, cols, 1e-6)
+        return ("rms_bwd_vec(+finalize)",
+                lambda: _lib.rms_norm_bwd(dx, dw, None, dy, x, w, rms, ws, rows, cols, cols, 1, cols, 1e-6),
+                3.0 * x.numel() * x.element_size())
+    if wl.name == "geglu":
+        x, w, b = tensors["x"].unsqueeze(0), tensors["w"], tensors["b"]
+        M, K = tensors["x"].shape
+        N = w.shape[0]
+        out = torch.empty(1, M, N // 2, device=dev, dtype=x.dtype)
+        sg = torch.empty(1, M, N, device=dev, dtype=x.dtype)
+        return ("geglu_fwd gemm", lambda: _lib.geglu_fwd(out, sg, x, w, b, False, False), 2.0 * M * N * K)
+    if wl.name.startswith("attention"):
+        q, k, v, dy = tensors["q"], tensors["k"], tensors["v"], tensors["dy"]
+        mask = tensors.get("mask")
+        causal = mask is None
+        B, H, S, D = q.shape
+        scale = D ** -0.5
+        out = torch.empty_like(q)
+        lse = torch.empty(B, H, S, device=dev)
+        dq, dk, dv = torch.empty_like(q), torch.empty_like(q), torch.empty_like(q)
+        ws = torch.empty(_lib.attention_bwd_workspace(B, H, S, D, q.dtype), dtype=torch.uint8, device=dev)
+        _lib.attention_fwd(out, lse, q, k, v, mask, causal, scale)
+        fwd = 4.0 * B * H * S * S * D * (0.5 if causal else 1.0)
+        return ("attention_bwd",
+                lambda: _lib.attention_bwd(dq, dk, dv, None, dy, q, k, v, out, lse, mask, ws, causal, scale),
+                2.5 * fwd)
+    raise KeyError(wl.name)
+
+
+def time_dominant(wl, tensors, steps, warmup):
+    label, launch, work = dominant_kernel(wl, tensors)
+    flush = torch.empty(2 * L2_BYTES, dtype=torch.uint8, device=tensors[wl.input_keys[0]].device)
+    need_flush = set_bytes(wl, tensors) < 2 * L2_BYTES
+    for _ in range(max(warmup, 3)):
+        launch()
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(steps):
+        if need_flush:
+            flush.zero_()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        launch()
+        b.record()
+        b.synchronize()
+        times.append(a.elapsed_time(b) / 1e3)
+    return label, work, statistics.mean(times), ("flush 252 MiB between launches" if need_flush else "inputs exceed L2")
+
+
+def cpu_run(wl, steps, warmup):
+    """The torch eager CPU oracle on a bounded sample; returns (rate, cores, sample text)."""
+    from oracle import torch_oracle
+
+    kw, text = CPU_SAMPLE[wl.name]
+    kw = dict(kw)
+    world = kw.pop("_world", 1)
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    tensors = wl.make(0, world, "cpu", **kw)
+    work = wl.work(tensors)
+    for _ in range(warmup):
+        wl.run(tensors, torch_oracle)
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        wl.run(tensors, torch_oracle)
+    dt = (time.perf_counter() - t0) / steps
+    return rate(wl, work, dt), cores, text, dt
+
+
+def run_reference(args, wl):
+    rank, _, world = dist_env()
+    if rank != 0:
+        return
+    steps = max(1, min(args.steps, 10))
+    warmup = max(1, min(args.warmup, 2))
+    value, cores, text, dt = cpu_run(wl, steps, warmup)
+    line = {
+        "impl": "reference", "metric": f"{wl.name} fwd+bwd {unit_of(wl)}", "value": value, "unit": unit_of(wl),
+        "n_gpus": args.gpus, "steps": steps, "warmup": warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": str(wl.dtype).replace("torch.", ""), "data": "synthetic",
+        "config": {"workload": wl.describe, "baseline_config": wl.config_index, "sample": text},
+        "cpu_baseline": {"value": value, "unit": unit_of(wl), "cores": cores, "kind": "port",
+                         "sample": text + "; torch eager CPU (the oracle the reference's tests use)"},
+        "e2e": {"value": value, "unit": unit_of(wl), "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def measure(wl, args, rank, world, device, with_cpu, sampler=None):
+    from trident_b200.workloads import owned_blocks
+
+    pk = peaks()
+    kw = {}
+    tensors = wl.make(rank, world, device, **kw)
+    work_local = wl.work(tensors)
+    nbytes = set_bytes(wl, tensors)
+    nsets = 1 if nbytes >= 2 * L2_BYTES else min(8, -(-3 * L2_BYTES // max(nbytes, 1)))
+    sets = [tensors] + [clone_set(tensors) for _ in range(nsets - 1)]
+    launches = launches_of_one_step(wl, tensors)
+    if sampler:
+        sampler.start()
+    secs, mode = time_device(wl, sets, args.steps, args.warmup, world, device)
+    clocks = sampler.stop() if sampler else None
+    work_total = reduce_sum(work_local, world, device)
+    value = rate(wl, work_total * args.steps, secs)
+    peak = pk["hbm_gbs"] if wl.bound == "hbm" else pk["bf16_tflops"]
+    del sets[1:]
+    label, kwork, ksecs, l2note = time_dominant(wl, tensors, min(args.steps, 20), args.warmup)
+    achieved = rate(wl, kwork, ksecs)
+    e2e_steps = max(3, min(args.steps, 10))
+    esecs, h2d, d2h = time_e2e(wl, tensors, e2e_steps, 1, world, device)
+    e2e_value = rate(wl, work_total * e2e_steps, esecs)
+    out = {
+        "metric": f"{wl.name} fwd+bwd {unit_of(wl)}", "value": value, "unit": unit_of(wl), "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": secs / args.steps * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": str(wl.dtype).replace("torch.", ""), "data": "synthetic",
+        "config": {"workload": wl.describe, "baseline_config": wl.config_index, "launch": mode,
+                   "l2": (f"rotating {nsets} input sets ({nsets * nbytes / 2**20:.0f} MiB)" if nsets > 1
+                          else f"inputs {nbytes / 2**20:.0f} MiB exceed L2"),
+                   "shard": f"rank {rank} owns blocks {list(owned_blocks(rank, world))} of 8"},
+        "step_frac_of_peak": value / (peak * world),
+        "roofline": {"bound": wl.bound, "kernel": label, "achieved": achieved, "peak": peak,
+                     "unit": unit_of(wl), "frac": achieved / peak, "traffic": None,
+                     "peak_source": pk["source"], "l2": l2note, "seconds_per_launch": ksecs},
+        "e2e": {"value": e2e_value, "unit": unit_of(wl), "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                "steps": e2e_steps},
+        "gpu_launches": launches * args.steps,
+        "gpu_launches_per_step": launches,
+    }
+    if clocks is not None:
+        out["clocks"] = clocks
+    if with_cpu:
+        v, cores, text, _ = cpu_run(wl, 2, 1)
+        out["cpu_baseline"] = {"value": v, "unit": unit_of(wl), "cores": cores, "kind": "port",
+                               "sample": text + "; torch eager CPU (the oracle the reference's tests use)"}
+    return out
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default=DEFAULT_WORKLOAD)
+    ap.add_argument("--others", default="auto",
+                    help="comma list of further workloads reported under 'workloads' (auto: all at N=1, none "
+                         "otherwise; 'none' to skip)")
+    args = ap.parse_args()
+
+    rank, local, world = dist_env()
+    if args.gpus > 1 and world == 1:
+        os.execvp(sys.executable, [sys.executable, "-m", "torch.distributed.run", "--nnodes=1",
+                                   f"--nproc-per-node={args.gpus}", "--master-addr", "127.0.0.1",
+                                   "--master-port", os.environ.get("MASTER_PORT", "29533"), __file__] + sys.argv[1:])
+
+    from trident_b200.workloads import WORKLOADS
+
+    wl = WORKLOADS[args.workload]
+    if args.impl == "reference":
+        run_reference(args, wl)
+        return
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the kernels have no CPU fallback")
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl", device_id=device)
+    from trident_b200 import _lib
+
+    _lib.load()
+    sampler = ClockSampler(local) if rank == 0 else None
+    line = measure(wl, args, rank, world, device, with_cpu=(rank == 0 and world == 1), sampler=sampler)
+    others = args.others
+    if others == "auto":
+        others = ",".join(n for n in WORKLOADS if n != wl.name) if world == 1 else "none"
+    extra = {}
+    if others != "none":
+        for name in [n for n in others.split(",") if n]:
+            try:
+                sub = measure(WORKLOADS[name], args, rank, world, device, with_cpu=(rank == 0 and world == 1))
+                extra[name] = {k: sub[k] for k in ("value", "unit", "ms_per_step", "step_frac_of_peak", "roofline",
+                                                   "e2e", "gpu_launches_per_step", "dtype") if k in sub}
+                if "cpu_baseline" in sub:
+                    extra[name]["cpu_baseline"] = sub["cpu_baseline"]
+                extra[name]["config"] = sub["config"]["workload"]
+            except Exception as exc:
+                extra[name] = {"error": repr(exc)}
+            torch.cuda.empty_cache()
+    if extra:
+        line["workloads"] = extra
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,149 @@
+"""Attention parity (cases of the reference's tests/test_attention.py, seeded, plus 16-bit
+cases at the benchmark head sizes)."""
+
+import pytest
+import torch
+
+import trident_b200 as trident
+from oracle import torch_oracle
+from tests import util
+
+pytestmark = pytest.mark.gpu
+
+SHAPES = [(4, 8, 128, 64, True), (4, 8, 256, 32, False), (1, 2, 64, 16, True), (2, 2, 512, 128, False)]
+
+
+@pytest.mark.parametrize("num_batches, num_heads, y_size, x_size, is_causal", SHAPES)
+def test_forward(num_batches, num_heads, y_size, x_size, is_causal, device):
+    q = util.randn(num_batches, num_heads, y_size, x_size, seed=1)
+    k = util.randn(num_batches, num_heads, y_size, x_size, seed=2)
+    v = util.randn(num_batches, num_heads, y_size, x_size, seed=3)
+    f = trident.function.scaled_dot_product_attention
+    got = f(q.to(device), k.to(device), v.to(device), is_causal=is_causal)
+    want = torch_oracle.scaled_dot_product_attention(q, k, v, is_causal=is_causal)
+    util.assert_close(got, want, 1e-5, 1e-4, "attention")
+
+    mask = util.randn(num_batches, num_heads, y_size, y_size, seed=4)
+    got = f(q.to(device), k.to(device), v.to(device), attn_mask=mask.to(device))
+    want = torch_oracle.scaled_dot_product_attention(q, k, v, attn_mask=mask)
+    util.assert_close(got, want, 1e-5, 1e-4, "attention mask")
+
+
+@pytest.mark.parametrize("num_batches, num_heads, y_size, x_size, is_causal", SHAPES[:3])
+def test_backward(num_batches, num_heads, y_size, x_size, is_causal, device):
+    q = util.rand(num_batches, num_heads, y_size, x_size, seed=1)
+    k = util.randn(num_batches, num_heads, y_size, x_size, seed=2)
+    v = util.randn(num_batches, num_heads, y_size, x_size, seed=3)
+    dy = util.randn(num_batches, num_heads, y_size, x_size, seed=5)
+    mask = util.randn(num_batches, num_heads, y_size, y_size, seed=4)
+
+    def train(fn, dev, use_mask):
+        i, j, l = (t.to(dev).requires_grad_(True) for t in (q, k, v))
+        if use_mask:
+            m = mask.to(dev).requires_grad_(True)
+            fn(i, j, l, attn_mask=m).backward(dy.to(dev))
+            return i.grad, j.grad, l.grad, m.grad
+        fn(i, j, l, is_causal=is_causal).backward(dy.to(dev))
+        return i.grad, j.grad, l.grad
+
+    for use_mask in (False, True):
+        got = train(trident.function.scaled_dot_product_attention, device, use_mask)
+        want = train(torch_oracle.scaled_dot_product_attention, "cpu", use_mask)
+        for g, w_, name in zip(got, want, ["dq", "dk", "dv", "dmask"]):
+            util.assert_close(g, w_, 1e-5, 2e-4, f"attention {name} mask={use_mask}")
+
+
+@pytest.mark.parametrize("mask_shape", ["b1ss", "11ss", "ss"])
+def test_broadcast_mask(mask_shape, device):
+    B, H, S, D = 2, 4, 128, 64
+    q, k, v, dy = (util.randn(B, H, S, D, seed=s) for s in (1, 2, 3, 5))
+    shape = {"b1ss": (B, 1, S, S), "11ss": (1, 1, S, S), "ss": (S, S)}[mask_shape]
+    mask = util.randn(*shape, seed=4)
+    drop = util.rand(*shape, seed=6) < 0.1
+    drop[..., 0] = False
+    mask = mask.masked_fill(drop, float("-inf"))
+
+    def train(fn, dev):
+        i, j, l = (t.to(dev).requires_grad_(True) for t in (q, k, v))
+        m = mask.to(dev).requires_grad_(True)
+        y = fn(i, j, l, attn_mask=m)
+        y.backward(dy.to(dev))
+        return y, i.grad, j.grad, l.grad, m.grad
+
+    got = train(trident.function.scaled_dot_product_attention, device)
+    want = train(torch_oracle.scaled_dot_product_attention, "cpu")
+    for g, w_, name in zip(got, want, ["y", "dq", "dk", "dv", "dmask"]):
+        util.assert_close(g, w_, 1e-5, 5e-4, f"broadcast {mask_shape} {name}")
+
+
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize(
+    "B, H, S, D, is_causal, masked",
+    [
+        (1, 2, 128, 128, True, False),
+        (2, 2, 256, 128, True, False),
+        (1, 2, 512, 64, False, False),
+        (2, 1, 256, 64, False, True),
+        (1, 1, 1024, 128, True, False),
+        (1, 2, 384 + 128, 64, True, False),
+    ],
+)
+def test_half_forward_backward(B, H, S, D, is_causal, masked, dt, device):
+    """bf16/fp16 at the benchmark head sizes: atol 1e-2 against the fp32 oracle."""
+    q, k, v, dy = (util.randn(B, H, S, D, seed=s, dtype=dt) for s in (1, 2, 3, 5))
+    mask = None
+    if masked:
+        drop = util.rand(B, 1, S, S, seed=6) < 0.1
+        drop[..., 0] = False
+        mask = torch.zeros(B, 1, S, S).masked_fill(drop, float("-inf")).to(dt)
+
+    def train(fn, dev, up):
+        i, j, l = (t.to(dev).to(up).requires_grad_(True) for t in (q, k, v))
+        if mask is not None:
+            y = fn(i, j, l, attn_mask=mask.to(dev).to(up))
+        else:
+            y = fn(i, j, l, is_causal=is_causal)
+        y.backward(dy.to(dev).to(up))
+        return y, i.grad, j.grad, l.grad
+
+    got = train(trident.function.scaled_dot_product_attention, device, dt)
+    want = train(torch_oracle.scaled_dot_product_attention, "cpu", torch.float32)
+    for g, w_, name in zip(got, want, ["y", "dq", "dk", "dv"]):
+        assert g.dtype == dt
+        err = util.max_abs(g, w_)
+        assert err <= 1e-2 or util.ulp_error(g, w_, dt) <= 2.0, f"{name}: max abs err {err}"
+
+
+def test_argument_errors(device):
+    f = trident.function.scaled_dot_product_attention
+    q = torch.randn(1, 1, 8, 16, device=device)
+    with pytest.raises(ValueError):
+        f(q[0], q[0], q[0])
+    with pytest.raises(ValueError):
+        f(q[:, :, :6], q[:, :, :6], q[:, :, :6])
+    with pytest.raises(ValueError):
+        f(q, q, q, attn_mask=torch.zeros(1, 1, 8, 8, device=device), is_causal=True)
+    with pytest.raises(ValueError):
+        f(q, q, q, attn_mask=torch.zeros(1, 1, 8, 8, device=device, dtype=torch.bool))
+
+
+@pytest.mark.parametrize(
+    "num_batches, num_heads, y_size, x_size, is_causal", [(1, 1, 1, 16, True), (1, 1, 1, 16, False)]
+)
+def test_attention(num_batches, num_heads, y_size, x_size, is_causal, device, dtype):
+    factory_kwargs = {"device": device, "dtype": dtype}
+    query = torch.rand(num_batches, num_heads, y_size, x_size, **factory_kwargs, requires_grad=True)
+    key = torch.randn_like(query, requires_grad=True)
+    value = torch.randn_like(query, requires_grad=True)
+    grad_output = torch.randn_like(query)
+
+    output = trident.function.scaled_dot_product_attention(query, key, value, is_causal=is_causal)
+    assert output is not None and output.dtype == dtype
+    output.backward(grad_output)
+    for t in (query, key, value):
+        assert t.grad is not None and t.grad.dtype == dtype
+
+    mask = torch.randn(num_batches, num_heads, y_size, y_size, **factory_kwargs, requires_grad=True)
+    output = trident.function.scaled_dot_product_attention(query, key, value, attn_mask=mask)
+    output.backward(grad_output)
+    assert mask.grad is not None and mask.grad.dtype == dtype

@@ -1,0 +1,303 @@
+// Library plumbing (error text, dispatch record, device attributes) and the extern "C"
+// entry points of Linear, GEGLU and Attention: validate, pick a kernel family, launch.
+#include <atomic>
+#include <cstring>
+#include <mutex>
+
+#include "attention.cuh"
+#include "common.cuh"
+#include "gemm_simt.cuh"
+#include "gemm_tc.cuh"
+
+namespace tb200 {
+
+static thread_local char g_error[512] = "";
+static thread_local const char* g_kernel = "";
+static thread_local int g_launches = 0;
+static int g_force_simt = 0;
+static std::atomic<long long> g_total_launches{0};
+
+void set_error(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_error, sizeof(g_error), fmt, ap);
+  va_end(ap);
+}
+void note_kernel(const char* family, int launches) {
+  g_kernel = family;
+  g_launches = launches;
+  g_total_launches += launches;
+}
+void add_launches(int launches) {
+  g_launches += launches;
+  g_total_launches += launches;
+}
+bool force_simt() { return g_force_simt != 0; }
+
+int sm_count() {
+  static int cached[64];
+  static std::once_flag once;
+  std::call_once(once, [] { std::memset(cached, 0, sizeof(cached)); });
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+    cudaGetLastError();
+    return 148;
+  }
+  if (cached[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) {
+      cudaGetLastError();
+      n = 148;
+    }
+    cached[dev] = n;
+  }
+  return cached[dev];
+}
+
+}  // namespace tb200
+
+using namespace tb200;
+
+extern "C" const char* tb200_last_error(void) { return g_error; }
+extern "C" int tb200_version(void) { return 100; }
+extern "C" const char* tb200_last_kernel(void) { return g_kernel; }
+extern "C" int tb200_last_launch_count(void) { return g_launches; }
+extern "C" int64_t tb200_total_launches(void) { return (int64_t)g_total_launches.load(); }
+extern "C" int tb200_set_force_simt(int on) {
+  const int old = g_force_simt;
+  g_force_simt = on;
+  return old;
+}
+
+extern "C" int tb200_device_check(int device) {
+  int major = 0;
+  cudaError_t e = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, device);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    set_error("device %d: %s", device, cudaGetErrorString(e));
+    return (int)e;
+  }
+  if (major != 10) {
+    set_error("device %d has compute capability %d.x; this library targets 10.x (sm_100a)", device,
+              major);
+    return TB200_ERR_UNSUPPORTED;
+  }
+  return 0;
+}
+
+// --------------------------------------------------------------------- Linear
+static int check_dims(const char* who, int64_t B, int64_t M, int64_t N, int64_t K) {
+  TB200_REQUIRE(B >= 0 && M >= 0 && N >= 0 && K >= 0, TB200_ERR_INVALID,
+                "%s: negative size (B=%lld M=%lld N=%lld K=%lld)", who, (long long)B, (long long)M,
+                (long long)N, (long long)K);
+  return 0;
+}
+
+extern "C" int tb200_linear_fwd(void* y, const void* x, const void* w, const void* bias, int64_t B,
+                                int64_t M, int64_t N, int64_t K, int64_t x_sb, int64_t x_sm,
+                                int64_t x_sk, int64_t w_sn, int64_t w_sk, int allow_tf32, int dtype,
+                                void* stream) {
+  (void)allow_tf32;  // fp32 operands are multiplied in full fp32 on the CUDA cores
+  TB200_REQUIRE(y && x && w, TB200_ERR_INVALID, "linear_fwd: null pointer");
+  if (int rc = check_dims("linear_fwd", B, M, N, K)) return rc;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (!force_simt()) {
+    // y[(b,m), n] = sum_k x[(b,m), k] w[n, k]: batch folds into M when x is batch-collapsible
+    if (dtype != TB200_F32 && x_sk == 1 && w_sk == 1 && (B == 1 || x_sb == M * x_sm)) {
+      TcGemmArgs g;
+      g.M = B * M; g.N = N; g.K = K;
+      g.a = x; g.a_ld = x_sm; g.a_kmajor = true;
+      g.b = w; g.b_ld = w_sn; g.b_kmajor = true;
+      g.c = y; g.c_ld = N; g.bias = bias;
+      if (tc_gemm_supported(g, dtype)) {
+        int rc = launch_gemm_tc(g, dtype, st);
+        if (rc == 0) note_kernel("gemm_tcgen05", 1);
+        return rc;
+      }
+    }
+  }
+  SimtGemmArgs g;
+  g.batches = B; g.M = M; g.N = N; g.K = K;
+  g.a_sb = x_sb; g.a_sm = x_sm; g.a_sk = x_sk;
+  g.b_sb = 0; g.b_sn = w_sn; g.b_sk = w_sk;
+  g.c_sb = M * N; g.c_sm = N; g.c_sn = 1;
+  int rc = launch_gemm_simt(y, x, w, bias, g, dtype, st);
+  if (rc == 0) note_kernel("gemm_simt", 1);
+  return rc;
+}
+
+extern "C" int tb200_linear_bwd_input(void* dx, const void* dy, const void* w, int64_t B, int64_t M,
+                                      int64_t N, int64_t K, int64_t dx_sb, int64_t dx_sm,
+                                      int64_t dx_sk, int64_t w_sn, int64_t w_sk, int allow_tf32,
+                                      int dtype, void* stream) {
+  (void)allow_tf32;
+  TB200_REQUIRE(dx && dy && w, TB200_ERR_INVALID, "linear_bwd_input: null pointer");
+  if (int rc = check_dims("linear_bwd_input", B, M, N, K)) return rc;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (!force_simt()) {
+    // dx[(b,m), k] = sum_n dy[(b,m), n] w[n, k]: the reduction index n is dy's contiguous
+    // one (K-major A) and w's row index (MN-major B).
+    if (dtype != TB200_F32 && dx_sk == 1 && w_sk == 1 && (B == 1 || dx_sb == M * dx_sm)) {
+      TcGemmArgs g;
+      g.M = B * M; g.N = K; g.K = N;
+      g.a = dy; g.a_ld = N; g.a_kmajor = true;
+      g.b = w; g.b_ld = w_sn; g.b_kmajor = false;
+      g.c = dx; g.c_ld = dx_sm;
+      if (tc_gemm_supported(g, dtype)) {
+        int rc = launch_gemm_tc(g, dtype, st);
+        if (rc == 0) note_kernel("gemm_tcgen05", 1);
+        return rc;
+      }
+    }
+  }
+  SimtGemmArgs g;
+  g.batches = B; g.M = M; g.N = K; g.K = N;
+  g.a_sb = M * N; g.a_sm = N; g.a_sk = 1;
+  g.b_sb = 0; g.b_sn = w_sk; g.b_sk = w_sn;
+  g.c_sb = dx_sb; g.c_sm = dx_sm; g.c_sn = dx_sk;
+  int rc = launch_gemm_simt(dx, dy, w, nullptr, g, dtype, st);
+  if (rc == 0) note_kernel("gemm_simt", 1);
+  return rc;
+}
+
+extern "C" int tb200_linear_bwd_weight(void* dw, const void* dy, const void* x, int64_t B,
+                                       int64_t M, int64_t N, int64_t K, int64_t x_sb, int64_t x_sm,
+                                       int64_t x_sk, int allow_tf32, int dtype, void* stream) {
+  (void)allow_tf32;
+  TB200_REQUIRE(dw && dy && x, TB200_ERR_INVALID, "linear_bwd_weight: null pointer");
+  if (int rc = check_dims("linear_bwd_weight", B, M, N, K)) return rc;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (!force_simt()) {
+    // dw[n, k] = sum_{(b,m)} dy[(b,m), n] x[(b,m), k]: both operands are MN-major.
+    if (dtype != TB200_F32 && x_sk == 1 && (B == 1 || x_sb == M * x_sm)) {
+      TcGemmArgs g;
+      g.M = N; g.N = K; g.K = B * M;
+      g.a = dy; g.a_ld = N; g.a_kmajor = false;
+      g.b = x; g.b_ld = x_sm; g.b_kmajor = false;
+      g.c = dw; g.c_ld = K;
+      if (tc_gemm_supported(g, dtype)) {
+        int rc = launch_gemm_tc(g, dtype, st);
+        if (rc == 0) note_kernel("gemm_tcgen05", 1);
+        return rc;
+      }
+    }
+  }
+  SimtGemmArgs g;
+  g.batches = 1; g.M = N; g.N = K; g.K = M; g.R = B;
+  g.a_sr = M * N; g.a_sm = 1; g.a_sk = N;
+  g.b_sr = x_sb; g.b_sn = x_sk; g.b_sk = x_sm;
+  g.c_sb = 0; g.c_sm = K; g.c_sn = 1;
+  int rc = launch_gemm_simt(dw, dy, x, nullptr, g, dtype, st);
+  if (rc == 0) note_kernel("gemm_simt", 1);
+  return rc;
+}
+
+// ---------------------------------------------------------------------- GEGLU
+extern "C" int tb200_geglu_fwd(void* out, void* state_gate, const void* x, const void* w,
+                               const void* bias, int64_t B, int64_t M, int64_t N, int64_t K,
+                               int64_t x_sb, int64_t x_sm, int64_t x_sk, int64_t w_sn, int64_t w_sk,
+                               int gelu_tanh, int allow_tf32, int dtype, void* stream) {
+  (void)allow_tf32;
+  TB200_REQUIRE(out && state_gate && x && w, TB200_ERR_INVALID, "geglu_fwd: null pointer");
+  if (int rc = check_dims("geglu_fwd", B, M, N, K)) return rc;
+  TB200_REQUIRE(N % 2 == 0, TB200_ERR_INVALID, "geglu_fwd: N=%lld must be even", (long long)N);
+  cudaStream_t st = (cudaStream_t)stream;
+  if (!force_simt()) {
+    if (dtype != TB200_F32 && x_sk == 1 && w_sk == 1 && (B == 1 || x_sb == M * x_sm)) {
+      TcGemmArgs g;
+      g.M = B * M; g.N = N; g.K = K;
+      g.a = x; g.a_ld = x_sm; g.a_kmajor = true;
+      g.b = w; g.b_ld = w_sn; g.b_kmajor = true;
+      g.c = state_gate; g.c_ld = N; g.bias = bias;
+      g.geglu_out = out; g.gelu_tanh = gelu_tanh;
+      if (tc_gemm_supported(g, dtype)) {
+        int rc = launch_gemm_tc(g, dtype, st);
+        if (rc == 0) note_kernel("gemm_tcgen05", 1);
+        return rc;
+      }
+    }
+  }
+  SimtGemmArgs g;
+  g.batches = B; g.M = M; g.N = N; g.K = K;
+  g.a_sb = x_sb; g.a_sm = x_sm; g.a_sk = x_sk;
+  g.b_sb = 0; g.b_sn = w_sn; g.b_sk = w_sk;
+  g.c_sb = M * N; g.c_sm = N; g.c_sn = 1;
+  int rc = launch_gemm_simt(state_gate, x, w, bias, g, dtype, st);
+  if (rc) return rc;
+  rc = launch_geglu_fwd_elementwise(out, state_gate, B * M, N / 2, gelu_tanh, dtype, st);
+  if (rc == 0) note_kernel("gemm_simt", 2);
+  return rc;
+}
+
+// ------------------------------------------------------------------ Attention
+static int fill_attn(AttnArgs* a, const char* who, int64_t B, int64_t H, int64_t S, int64_t D,
+                     const int64_t* qs, const int64_t* ks, const int64_t* vs, const int64_t* os,
+                     const void* mask, const int64_t* ms, int is_causal, float scale) {
+  TB200_REQUIRE(B > 0 && H > 0 && S > 0, TB200_ERR_INVALID, "%s: bad shape", who);
+  TB200_REQUIRE(D == 16 || D == 32 || D == 64 || D == 128, TB200_ERR_UNSUPPORTED,
+                "%s: head size %lld not in {16,32,64,128}", who, (long long)D);
+  TB200_REQUIRE(qs && ks && vs && os, TB200_ERR_INVALID, "%s: null stride array", who);
+  TB200_REQUIRE(!(mask && is_causal), TB200_ERR_INVALID, "%s: mask and is_causal are exclusive",
+                who);
+  TB200_REQUIRE(!mask || ms, TB200_ERR_INVALID, "%s: mask without strides", who);
+  a->B = B; a->H = H; a->S = S; a->D = D;
+  for (int i = 0; i < 4; ++i) {
+    a->qs[i] = qs[i]; a->ks[i] = ks[i]; a->vs[i] = vs[i]; a->os[i] = os[i];
+    a->ms[i] = mask ? ms[i] : 0;
+  }
+  a->causal = is_causal ? 1 : 0;
+  a->scale = scale;
+  return 0;
+}
+
+extern "C" int tb200_attention_fwd(void* out, float* lse, const void* q, const void* k,
+                                   const void* v, const void* mask, int64_t B, int64_t H, int64_t S,
+                                   int64_t D, const int64_t* q_strides, const int64_t* k_strides,
+                                   const int64_t* v_strides, const int64_t* out_strides,
+                                   const int64_t* mask_strides, int is_causal, float softmax_scale,
+                                   int dtype, void* stream) {
+  TB200_REQUIRE(out && lse && q && k && v, TB200_ERR_INVALID, "attention_fwd: null pointer");
+  AttnArgs a;
+  if (int rc = fill_attn(&a, "attention_fwd", B, H, S, D, q_strides, k_strides, v_strides,
+                         out_strides, mask, mask_strides, is_causal, softmax_scale))
+    return rc;
+  cudaStream_t st = (cudaStream_t)stream;
+  int rc = launch_attn_fwd_simt(out, lse, q, k, v, mask, a, dtype, st);
+  if (rc == 0) note_kernel("attn_simt", 1);
+  return rc;
+}
+
+extern "C" size_t tb200_attention_bwd_workspace(int64_t B, int64_t H, int64_t S, int64_t D,
+                                                int dtype) {
+  if (B <= 0 || H <= 0 || S <= 0 || D <= 0) return 0;
+  size_t delta = (size_t)B * H * S * sizeof(float);
+  delta = (delta + 255) & ~(size_t)255;
+  size_t dq_acc = dtype == TB200_F32 ? 0 : (size_t)B * H * S * D * sizeof(float);
+  return delta + dq_acc;
+}
+
+extern "C" int tb200_attention_bwd(void* dq, void* dk, void* dv, void* dmask, const void* dout,
+                                   const void* q, const void* k, const void* v, const void* out,
+                                   const float* lse, const void* mask, void* workspace,
+                                   size_t workspace_bytes, int64_t B, int64_t H, int64_t S,
+                                   int64_t D, const int64_t* q_strides, const int64_t* k_strides,
+                                   const int64_t* v_strides, const int64_t* out_strides,
+                                   const int64_t* mask_strides, int is_causal, float softmax_scale,
+                                   int dtype, void* stream) {
+  TB200_REQUIRE(dq && dk && dv && dout && q && k && v && out && lse && workspace, TB200_ERR_INVALID,
+                "attention_bwd: null pointer");
+  TB200_REQUIRE(!dmask || mask, TB200_ERR_INVALID, "attention_bwd: dmask without mask");
+  AttnArgs a;
+  if (int rc = fill_attn(&a, "attention_bwd", B, H, S, D, q_strides, k_strides, v_strides,
+                         out_strides, mask, mask_strides, is_causal, softmax_scale))
+    return rc;
+  TB200_REQUIRE(workspace_bytes >= (size_t)B * H * S * sizeof(float), TB200_ERR_WORKSPACE,
+                "attention_bwd: workspace too small");
+  cudaStream_t st = (cudaStream_t)stream;
+  float* delta = (float*)workspace;
+  int rc = launch_attn_delta(delta, out, dout, a, dtype, st);
+  if (rc) return rc;
+  rc = launch_attn_bwd_simt(dq, dk, dv, dmask, dout, q, k, v, lse, delta, mask, a, dtype, st);
+  if (rc == 0) note_kernel("attn_simt", 3);
+  return rc;
+}

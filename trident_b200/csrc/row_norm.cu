@@ -1,0 +1,564 @@
+// LayerNorm and RMSNorm, forward and backward, as single-pass HBM-bound row kernels.
+//
+// Math (all reductions and statistics in fp32, outputs rounded once):
+//   LayerNorm  fwd: mu = mean(x); var = mean((x-mu)^2); rstd = rsqrt(var+eps);
+//                   y = (x-mu)*rstd*w + b                       (w, b optional)
+//              bwd: g = dy*w; c1 = mean(g*xhat); c2 = mean(g);
+//                   dx = rstd*(g - xhat*c1 - c2); dw = sum_rows dy*xhat; db = sum_rows dy
+//     (restates trident/kernel/layer_norm.py:72-126 and :188-246 plus the torch.sum
+//      calls of trident/operation/layer_norm.py:112-122)
+//   RMSNorm    fwd: rms = sqrt(sum_{i<P} x_i^2 / P); y = x/(rms+eps)*w (+ b)
+//              bwd: g = dy*w; s = sum_i g_i*x_i;
+//                   dx_i = g_i/(rms+eps) - [i<P] x_i*s / (P*rms*(rms+eps)^2);
+//                   dw = sum_rows dy*x/(rms+eps); db = sum_rows dy
+//     (restates trident/kernel/rms_norm.py:74-117 and :190-232, with the exact derivative
+//      of the forward expression; eps sits outside the square root as in
+//      tests/test_rms_norm.py:22-39)
+//
+// Algorithmic HBM bytes per element of the [rows, cols] problem: forward 2*e (read x,
+// write y), backward 3*e (read x and dy, write dx); the weight-gradient column sums add
+// one fp32 partial row per CTA (grid bounded by the SM count), reduced by a second small
+// kernel.
+#include "row_common.cuh"
+
+namespace tb200 {
+
+// ------------------------------------------------------------------ LayerNorm fwd
+template <typename T, int CHUNKS, bool CTA_ROW>
+__global__ void __launch_bounds__(CTA_ROW ? 512 : 256)
+    ln_fwd_vec(T* __restrict__ y, float* __restrict__ mean, float* __restrict__ rstd,
+               const T* __restrict__ x, const T* __restrict__ w, const T* __restrict__ b,
+               int64_t rows, int cols, float eps) {
+  constexpr int VEC = Traits<T>::VEC;
+  __shared__ float slot[64];
+  int phase = 0;
+  RowThread<CTA_ROW> rt;
+  const float inv_n = 1.f / (float)cols;
+  for (int64_t row = rt.first_row(); row < rows; row += rt.row_step()) {
+    float xs[CHUNKS][VEC];
+    load_row<T, CHUNKS, CTA_ROW>(xs, x + row * cols, cols, rt);
+    float s = 0.f;
+#pragma unroll
+    for (int c = 0; c < CHUNKS; ++c)
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) s += xs[c][i];
+    const float mu = row_reduce<CTA_ROW, false>(s, slot, phase) * inv_n;
+    float v = 0.f;
+#pragma unroll
+    for (int c = 0; c < CHUNKS; ++c) {
+      const bool in = rt.template col<VEC>(c) < cols;
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) {
+        const float d = xs[c][i] - mu;
+        v += in ? d * d : 0.f;
+      }
+    }
+    const float var = row_reduce<CTA_ROW, false>(v, slot, phase) * inv_n;
+    const float rs = rsqrtf(var + eps);
+#pragma unroll
+    for (int c = 0; c < CHUNKS; ++c) {
+      const int col = rt.template col<VEC>(c);
+      if (col < cols) {
+        float ws[VEC], bs[VEC];
+        if (w) unpack<T>(ld_cached(w + col), ws);
+        if (b) unpack<T>(ld_cached(b + col), bs);
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) {
+          float o = (xs[c][i] - mu) * rs;
+          if (w) o *= ws[i];
+          if (b) o += bs[i];
+          xs[c][i] = o;
+        }
+      }
+    }
+    store_row<T, CHUNKS, CTA_ROW>(y + row * cols, xs, cols, rt);
+    if (rt.tid == 0) {
+      mean[row] = mu;
+      rstd[row] = rs;
+    }
+  }
+}
+
+template <typename T>
+__global__ void ln_fwd_generic(T* y, float* mean, float* rstd, const T* x, const T* w, const T* b,
+                               int64_t rows, int64_t cols, float eps) {
+  const int lane = threadIdx.x & 31;
+  const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const T* xr = x + row * cols;
+  float s = 0.f;
+  for (int64_t i = lane; i < cols; i += 32) s += Traits<T>::to_f(xr[i]);
+  const float mu = warp_sum(s) / (float)cols;
+  float v = 0.f;
+  for (int64_t i = lane; i < cols; i += 32) {
+    const float d = Traits<T>::to_f(xr[i]) - mu;
+    v += d * d;
+  }
+  const float rs = rsqrtf(warp_sum(v) / (float)cols + eps);
+  T* yr = y + row * cols;
+  for (int64_t i = lane; i < cols; i += 32) {
+    float o = (Traits<T>::to_f(xr[i]) - mu) * rs;
+    if (w) o *= Traits<T>::to_f(w[i]);
+    if (b) o += Traits<T>::to_f(b[i]);
+    yr[i] = Traits<T>::from_f(o);
+  }
+  if (lane == 0) {
+    mean[row] = mu;
+    rstd[row] = rs;
+  }
+}
+
+// ------------------------------------------------------------------ LayerNorm bwd
+template <typename T, int CHUNKS, bool CTA_ROW>
+__global__ void __launch_bounds__(CTA_ROW ? 512 : 256)
+    ln_bwd_vec(T* __restrict__ dx, float* __restrict__ partial, const T* __restrict__ dy,
+               const T* __restrict__ x, const T* __restrict__ w, const float* __restrict__ mean,
+               const float* __restrict__ rstd, int64_t rows, int cols, int want_cols) {
+  constexpr int VEC = Traits<T>::VEC;
+  __shared__ float slot[64];
+  __shared__ __align__(16) float colbuf[CTA_ROW ? 4 : 2 * 1024];
+  int phase = 0;
+  RowThread<CTA_ROW> rt;
+  const float inv_n = 1.f / (float)cols;
+  float acc_w[CHUNKS][VEC], acc_b[CHUNKS][VEC], ws[CHUNKS][VEC];
+#pragma unroll
+  for (int c = 0; c < CHUNKS; ++c) {
+    const int col = rt.template col<VEC>(c);
+    if (w && col < cols) unpack<T>(ld_cached(w + col), ws[c]);
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) {
+      acc_w[c][i] = 0.f;
+      acc_b[c][i] = 0.f;
+      if (!w || col >= cols) ws[c][i] = 1.f;
+    }
+  }
+  for (int64_t row = rt.first_row(); row < rows; row += rt.row_step()) {
+    float xs[CHUNKS][VEC], gs[CHUNKS][VEC];
+    load_row<T, CHUNKS, CTA_ROW>(xs, x + row * cols, cols, rt);
+    load_row<T, CHUNKS, CTA_ROW>(gs, dy + row * cols, cols, rt);
+    const float mu = mean[row], rs = rstd[row];
+    float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+    for (int c = 0; c < CHUNKS; ++c) {
+      const bool in = rt.template col<VEC>(c) < cols;
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) {
+        const float xh = in ? (xs[c][i] - mu) * rs : 0.f;
+        const float d = gs[c][i];
+        acc_w[c][i] += d * xh;
+        acc_b[c][i] += d;
+        const float g = d * ws[c][i];
+        xs[c][i] = xh;
+        gs[c][i] = g;
+        s1 += g * xh;
+        s2 += g;
+      }
+    }
+    const float c1 = row_reduce<CTA_ROW, false>(s1, slot, phase) * inv_n;
+    const float c2 = row_reduce<CTA_ROW, false>(s2, slot, phase) * inv_n;
+#pragma unroll
+    for (int c = 0; c < CHUNKS; ++c)
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) xs[c][i] = rs * (gs[c][i] - xs[c][i] * c1 - c2);
+    store_row<T, CHUNKS, CTA_ROW>(dx + row * cols, xs, cols, rt);
+  }
+  if (want_cols)
+    write_col_partials<CHUNKS, VEC, CTA_ROW>(partial + (int64_t)blockIdx.x * 2 * cols, cols, acc_w,
+                                             acc_b, rt, colbuf);
+}
+
+template <typename T>
+__global__ void ln_bwd_dx_generic(T* dx, const T* dy, const T* x, const T* w, const float* mean,
+                                  const float* rstd, int64_t rows, int64_t cols) {
+  const int lane = threadIdx.x & 31;
+  const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const T* xr = x + row * cols;
+  const T* gr = dy + row * cols;
+  const float mu = mean[row], rs = rstd[row];
+  float s1 = 0.f, s2 = 0.f;
+  for (int64_t i = lane; i < cols; i += 32) {
+    const float xh = (Traits<T>::to_f(xr[i]) - mu) * rs;
+    const float g = Traits<T>::to_f(gr[i]) * (w ? Traits<T>::to_f(w[i]) : 1.f);
+    s1 += g * xh;
+    s2 += g;
+  }
+  const float c1 = warp_sum(s1) / (float)cols, c2 = warp_sum(s2) / (float)cols;
+  for (int64_t i = lane; i < cols; i += 32) {
+    const float xh = (Traits<T>::to_f(xr[i]) - mu) * rs;
+    const float g = Traits<T>::to_f(gr[i]) * (w ? Traits<T>::to_f(w[i]) : 1.f);
+    dx[row * cols + i] = Traits<T>::from_f(rs * (g - xh * c1 - c2));
+  }
+}
+
+// One thread per column walks all rows (coalesced across the warp). `scale_kind`:
+// 0 = LayerNorm (xhat = (x-mean)*rstd), 1 = RMSNorm (xhat = x/(rms+eps)).
+template <typename T>
+__global__ void norm_bwd_cols_generic(T* dw, T* db, const T* dy, const T* x, const float* stat_a,
+                                      const float* stat_b, int64_t rows, int64_t cols,
+                                      int64_t x_rs, int64_t x_cs, float eps, int scale_kind) {
+  const int64_t col = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (col >= cols) return;
+  float aw = 0.f, ab = 0.f;
+  for (int64_t r = 0; r < rows; ++r) {
+    const float d = Traits<T>::to_f(dy[r * cols + col]);
+    const float xv = Traits<T>::to_f(x[r * x_rs + col * x_cs]);
+    const float xh = scale_kind == 0 ? (xv - stat_a[r]) * stat_b[r] : xv / (stat_a[r] + eps);
+    aw += d * xh;
+    ab += d;
+  }
+  if (dw) dw[col] = Traits<T>::from_f(aw);
+  if (db) db[col] = Traits<T>::from_f(ab);
+}
+
+// ------------------------------------------------------------------ RMSNorm fwd
+template <typename T, int CHUNKS, bool CTA_ROW>
+__global__ void __launch_bounds__(CTA_ROW ? 512 : 256)
+    rms_fwd_vec(T* __restrict__ y, float* __restrict__ rms, const T* __restrict__ x,
+                const T* __restrict__ w, const T* __restrict__ b, int64_t rows, int cols,
+                int64_t row_stride, int partial, float eps) {
+  constexpr int VEC = Traits<T>::VEC;
+  __shared__ float slot[64];
+  int phase = 0;
+  RowThread<CTA_ROW> rt;
+  for (int64_t row = rt.first_row(); row < rows; row += rt.row_step()) {
+    float xs[CHUNKS][VEC];
+    load_row<T, CHUNKS, CTA_ROW>(xs, x + row * row_stride, cols, rt);
+    float s = 0.f;
+#pragma unroll
+    for (int c = 0; c < CHUNKS; ++c) {
+      const int col = rt.template col<VEC>(c);
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) s += (col + i < partial) ? xs[c][i] * xs[c][i] : 0.f;
+    }
+    const float r = sqrtf(row_reduce<CTA_ROW, false>(s, slot, phase) / (float)partial);
+    const float inv = 1.f / (r + eps);
+#pragma unroll
+    for (int c = 0; c < CHUNKS; ++c) {
+      const int col = rt.template col<VEC>(c);
+      if (col < cols) {
+        float ws[VEC], bs[VEC];
+        unpack<T>(ld_cached(w + col), ws);
+        if (b) unpack<T>(ld_cached(b + col), bs);
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) {
+          float o = xs[c][i] * inv * ws[i];
+          if (b) o += bs[i];
+          xs[c][i] = o;
+        }
+      }
+    }
+    store_row<T, CHUNKS, CTA_ROW>(y + row * cols, xs, cols, rt);
+    if (rt.tid == 0) rms[row] = r;
+  }
+}
+
+template <typename T>
+__global__ void rms_fwd_generic(T* y, float* rms, const T* x, const T* w, const T* b, int64_t rows,
+                                int64_t cols, int64_t rs_, int64_t cs_, int64_t partial, float eps) {
+  const int lane = threadIdx.x & 31;
+  const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const T* xr = x + row * rs_;
+  float s = 0.f;
+  for (int64_t i = lane; i < partial; i += 32) {
+    const float v = Traits<T>::to_f(xr[i * cs_]);
+    s += v * v;
+  }
+  const float r = sqrtf(warp_sum(s) / (float)partial);
+  const float inv = 1.f / (r + eps);
+  for (int64_t i = lane; i < cols; i += 32) {
+    float o = Traits<T>::to_f(xr[i * cs_]) * inv * Traits<T>::to_f(w[i]);
+    if (b) o += Traits<T>::to_f(b[i]);
+    y[row * cols + i] = Traits<T>::from_f(o);
+  }
+  if (lane == 0) rms[row] = r;
+}
+
+// ------------------------------------------------------------------ RMSNorm bwd
+template <typename T, int CHUNKS, bool CTA_ROW>
+__global__ void __launch_bounds__(CTA_ROW ? 512 : 256)
+    rms_bwd_vec(T* __restrict__ dx, float* __restrict__ partial_ws, const T* __restrict__ dy,
+                const T* __restrict__ x, const T* __restrict__ w, const float* __restrict__ rms,
+                int64_t rows, int cols, int64_t row_stride, int partial, float eps) {
+  constexpr int VEC = Traits<T>::VEC;
+  __shared__ float slot[64];
+  __shared__ __align__(16) float colbuf[CTA_ROW ? 4 : 2 * 1024];
+  int phase = 0;
+  RowThread<CTA_ROW> rt;
+  float acc_w[CHUNKS][VEC], acc_b[CHUNKS][VEC], ws[CHUNKS][VEC];
+#pragma unroll
+  for (int c = 0; c < CHUNKS; ++c) {
+    const int col = rt.template col<VEC>(c);
+    if (col < cols) unpack<T>(ld_cached(w + col), ws[c]);
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) {
+      acc_w[c][i] = 0.f;
+      acc_b[c][i] = 0.f;
+      if (col >= cols) ws[c][i] = 0.f;
+    }
+  }
+  for (int64_t row = rt.first_row(); row < rows; row += rt.row_step()) {
+    float xs[CHUNKS][VEC], gs[CHUNKS][VEC];
+    load_row<T, CHUNKS, CTA_ROW>(xs, x + row * row_stride, cols, rt);
+    load_row<T, CHUNKS, CTA_ROW>(gs, dy + row * cols, cols, rt);
+    const float r = rms[row];
+    const float inv = 1.f / (r + eps);
+    float s = 0.f;
+#pragma unroll
+    for (int c = 0; c < CHUNKS; ++c)
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) {
+        const float d = gs[c][i];
+        acc_w[c][i] += d * xs[c][i] * inv;
+        acc_b[c][i] += d;
+        const float g = d * ws[c][i];
+        gs[c][i] = g;
+        s += g * xs[c][i];
+      }
+    s = row_reduce<CTA_ROW, false>(s, slot, phase);
+    // second term vanishes for an all-zero row (rms == 0)
+    const float k = r > 0.f ? s * inv * inv / ((float)partial * r) : 0.f;
+#pragma unroll
+    for (int c = 0; c < CHUNKS; ++c) {
+      const int col = rt.template col<VEC>(c);
+#pragma unroll
+      for (int i = 0; i < VEC; ++i)
+        xs[c][i] = gs[c][i] * inv - ((col + i < partial) ? xs[c][i] * k : 0.f);
+    }
+    store_row<T, CHUNKS, CTA_ROW>(dx + row * cols, xs, cols, rt);
+  }
+  write_col_partials<CHUNKS, VEC, CTA_ROW>(partial_ws + (int64_t)blockIdx.x * 2 * cols, cols, acc_w,
+                                           acc_b, rt, colbuf);
+}
+
+template <typename T>
+__global__ void rms_bwd_dx_generic(T* dx, const T* dy, const T* x, const T* w, const float* rms,
+                                   int64_t rows, int64_t cols, int64_t rs_, int64_t cs_,
+                                   int64_t partial, float eps) {
+  const int lane = threadIdx.x & 31;
+  const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const T* xr = x + row * rs_;
+  const float r = rms[row];
+  const float inv = 1.f / (r + eps);
+  float s = 0.f;
+  for (int64_t i = lane; i < cols; i += 32)
+    s += Traits<T>::to_f(dy[row * cols + i]) * Traits<T>::to_f(w[i]) * Traits<T>::to_f(xr[i * cs_]);
+  s = warp_sum(s);
+  const float k = r > 0.f ? s * inv * inv / ((float)partial * r) : 0.f;
+  for (int64_t i = lane; i < cols; i += 32) {
+    const float g = Traits<T>::to_f(dy[row * cols + i]) * Traits<T>::to_f(w[i]);
+    const float xv = Traits<T>::to_f(xr[i * cs_]);
+    dx[row * cols + i] = Traits<T>::from_f(g * inv - (i < partial ? xv * k : 0.f));
+  }
+}
+
+// ------------------------------------------------------------------ host side
+static size_t col_partial_bytes(int64_t cols) {
+  // one [2, cols] fp32 row per CTA of the bounded grid (at most 4 CTAs per SM)
+  return (size_t)sm_count() * 4 * 2 * (size_t)cols * sizeof(float);
+}
+
+template <typename T>
+static int finalize_cols(T* da, T* db, const float* partial, int nparts, int64_t cols,
+                         cudaStream_t st) {
+  dim3 grid((unsigned)ceil_div(cols, 32), 2), block(32, 32);
+  colsum_finalize_kernel<T><<<grid, block, 0, st>>>(da, db, partial, nparts, (int)cols);
+  return launch_status("colsum_finalize");
+}
+
+}  // namespace tb200
+
+using namespace tb200;
+
+extern "C" int tb200_layer_norm_fwd(void* y, float* mean, float* rstd, const void* x,
+                                    const void* weight, const void* bias, int64_t rows,
+                                    int64_t cols, float eps, int dtype, void* stream) {
+  TB200_REQUIRE(y && mean && rstd && x, TB200_ERR_INVALID, "layer_norm_fwd: null pointer");
+  TB200_REQUIRE(rows >= 0 && cols > 0, TB200_ERR_INVALID, "layer_norm_fwd: bad shape %lld x %lld",
+                (long long)rows, (long long)cols);
+  if (rows == 0) return 0;
+  cudaStream_t st = (cudaStream_t)stream;
+  return dispatch_dtype(dtype, [&](auto tag) -> int {
+    using T = decltype(tag);
+    const bool ok = aligned16(y) && aligned16(x) && (!weight || aligned16(weight)) &&
+                    (!bias || aligned16(bias)) && cols < (1 << 30);
+    RowPlan p = plan_rows<T>(cols, ok);
+    if (p.vec) {
+      const int64_t grid = ceil_div(rows, p.rows_per_cta);
+      int rc = dispatch_plan<T>(p, [&](auto c, auto cta) -> int {
+        ln_fwd_vec<T, decltype(c)::value, decltype(cta)::value>
+            <<<(unsigned)grid, p.threads, 0, st>>>((T*)y, mean, rstd, (const T*)x,
+                                                   (const T*)weight, (const T*)bias, rows,
+                                                   (int)cols, eps);
+        return launch_status("ln_fwd_vec");
+      });
+      if (rc == 0) note_kernel("row_vec", 1);
+      return rc;
+    }
+    ln_fwd_generic<T><<<(unsigned)ceil_div(rows, 4), 128, 0, st>>>(
+        (T*)y, mean, rstd, (const T*)x, (const T*)weight, (const T*)bias, rows, cols, eps);
+    int rc = launch_status("ln_fwd_generic");
+    if (rc == 0) note_kernel("row_generic", 1);
+    return rc;
+  });
+}
+
+extern "C" size_t tb200_layer_norm_bwd_workspace(int64_t rows, int64_t cols) {
+  (void)rows;
+  return cols > 0 ? col_partial_bytes(cols) : 0;
+}
+
+extern "C" int tb200_layer_norm_bwd(void* dx, void* dweight, void* dbias, const void* dy,
+                                    const void* x, const void* weight, const float* mean,
+                                    const float* rstd, void* workspace, size_t workspace_bytes,
+                                    int64_t rows, int64_t cols, int dtype, void* stream) {
+  TB200_REQUIRE(dx && dy && x && mean && rstd, TB200_ERR_INVALID, "layer_norm_bwd: null pointer");
+  TB200_REQUIRE(rows >= 0 && cols > 0, TB200_ERR_INVALID, "layer_norm_bwd: bad shape");
+  cudaStream_t st = (cudaStream_t)stream;
+  const bool want_cols = dweight || dbias;
+  return dispatch_dtype(dtype, [&](auto tag) -> int {
+    using T = decltype(tag);
+    const bool ok = aligned16(dx) && aligned16(dy) && aligned16(x) &&
+                    (!weight || aligned16(weight)) && cols < (1 << 30) &&
+                    (!want_cols || (workspace && aligned16(workspace)));
+    RowPlan p = plan_rows<T>(cols, ok, max_chunks<T>() / 2);
+    if (p.vec && rows > 0) {
+      const int64_t grid = persistent_grid(p, rows);
+      if (want_cols)
+        TB200_REQUIRE(workspace_bytes >= (size_t)grid * 2 * cols * sizeof(float),
+                      TB200_ERR_WORKSPACE, "layer_norm_bwd: workspace too small");
+      int rc = dispatch_plan<T>(p, [&](auto c, auto cta) -> int {
+        ln_bwd_vec<T, decltype(c)::value, decltype(cta)::value>
+            <<<(unsigned)grid, p.threads, 0, st>>>((T*)dx, (float*)workspace, (const T*)dy,
+                                                   (const T*)x, (const T*)weight, mean, rstd, rows,
+                                                   (int)cols, want_cols ? 1 : 0);
+        return launch_status("ln_bwd_vec");
+      });
+      if (rc) return rc;
+      if (want_cols) {
+        rc = finalize_cols<T>((T*)dweight, (T*)dbias, (const float*)workspace, (int)grid, cols, st);
+        if (rc) return rc;
+      }
+      note_kernel("row_vec", want_cols ? 2 : 1);
+      return 0;
+    }
+    int launches = 0;
+    if (rows > 0) {
+      ln_bwd_dx_generic<T><<<(unsigned)ceil_div(rows, 4), 128, 0, st>>>(
+          (T*)dx, (const T*)dy, (const T*)x, (const T*)weight, mean, rstd, rows, cols);
+      int rc = launch_status("ln_bwd_dx_generic");
+      if (rc) return rc;
+      ++launches;
+    }
+    if (want_cols) {
+      norm_bwd_cols_generic<T><<<(unsigned)ceil_div(cols, 128), 128, 0, st>>>(
+          (T*)dweight, (T*)dbias, (const T*)dy, (const T*)x, mean, rstd, rows, cols, cols, 1, 0.f,
+          0);
+      int rc = launch_status("norm_bwd_cols_generic");
+      if (rc) return rc;
+      ++launches;
+    }
+    note_kernel("row_generic", launches);
+    return 0;
+  });
+}
+
+extern "C" int tb200_rms_norm_fwd(void* y, float* rms, const void* x, const void* weight,
+                                  const void* bias, int64_t rows, int64_t cols, int64_t row_stride,
+                                  int64_t col_stride, int64_t partial_cols, float eps, int dtype,
+                                  void* stream) {
+  TB200_REQUIRE(y && rms && x && weight, TB200_ERR_INVALID, "rms_norm_fwd: null pointer");
+  TB200_REQUIRE(rows >= 0 && cols > 0, TB200_ERR_INVALID, "rms_norm_fwd: bad shape");
+  TB200_REQUIRE(partial_cols > 0 && partial_cols <= cols, TB200_ERR_INVALID,
+                "rms_norm_fwd: partial_cols %lld outside (0, %lld]", (long long)partial_cols,
+                (long long)cols);
+  if (rows == 0) return 0;
+  cudaStream_t st = (cudaStream_t)stream;
+  return dispatch_dtype(dtype, [&](auto tag) -> int {
+    using T = decltype(tag);
+    constexpr int VEC = Traits<T>::VEC;
+    const bool ok = aligned16(y) && aligned16(x) && aligned16(weight) &&
+                    (!bias || aligned16(bias)) && col_stride == 1 && row_stride % VEC == 0 &&
+                    row_stride >= cols && cols < (1 << 30);
+    RowPlan p = plan_rows<T>(cols, ok);
+    if (p.vec) {
+      const int64_t grid = ceil_div(rows, p.rows_per_cta);
+      int rc = dispatch_plan<T>(p, [&](auto c, auto cta) -> int {
+        rms_fwd_vec<T, decltype(c)::value, decltype(cta)::value>
+            <<<(unsigned)grid, p.threads, 0, st>>>((T*)y, rms, (const T*)x, (const T*)weight,
+                                                   (const T*)bias, rows, (int)cols, row_stride,
+                                                   (int)partial_cols, eps);
+        return launch_status("rms_fwd_vec");
+      });
+      if (rc == 0) note_kernel("row_vec", 1);
+      return rc;
+    }
+    rms_fwd_generic<T><<<(unsigned)ceil_div(rows, 4), 128, 0, st>>>(
+        (T*)y, rms, (const T*)x, (const T*)weight, (const T*)bias, rows, cols, row_stride,
+        col_stride, partial_cols, eps);
+    int rc = launch_status("rms_fwd_generic");
+    if (rc == 0) note_kernel("row_generic", 1);
+    return rc;
+  });
+}
+
+extern "C" size_t tb200_rms_norm_bwd_workspace(int64_t rows, int64_t cols) {
+  (void)rows;
+  return cols > 0 ? col_partial_bytes(cols) : 0;
+}
+
+extern "C" int tb200_rms_norm_bwd(void* dx, void* dweight, void* dbias, const void* dy,
+                                  const void* x, const void* weight, const float* rms,
+                                  void* workspace, size_t workspace_bytes, int64_t rows,
+                                  int64_t cols, int64_t row_stride, int64_t col_stride,
+                                  int64_t partial_cols, float eps, int dtype, void* stream) {
+  TB200_REQUIRE(dx && dweight && dy && x && weight && rms, TB200_ERR_INVALID,
+                "rms_norm_bwd: null pointer");
+  TB200_REQUIRE(rows >= 0 && cols > 0, TB200_ERR_INVALID, "rms_norm_bwd: bad shape");
+  TB200_REQUIRE(partial_cols > 0 && partial_cols <= cols, TB200_ERR_INVALID,
+                "rms_norm_bwd: partial_cols outside (0, cols]");
+  cudaStream_t st = (cudaStream_t)stream;
+  return dispatch_dtype(dtype, [&](auto tag) -> int {
+    using T = decltype(tag);
+    constexpr int VEC = Traits<T>::VEC;
+    const bool ok = aligned16(dx) && aligned16(dy) && aligned16(x) && aligned16(weight) &&
+                    col_stride == 1 && row_stride % VEC == 0 && row_stride >= cols &&
+                    cols < (1 << 30) && workspace && aligned16(workspace);
+    RowPlan p = plan_rows<T>(cols, ok, max_chunks<T>() / 2);
+    if (p.vec && rows > 0) {
+      const int64_t grid = persistent_grid(p, rows);
+      TB200_REQUIRE(workspace_bytes >= (size_t)grid * 2 * cols * sizeof(float), TB200_ERR_WORKSPACE,
+                    "rms_norm_bwd: workspace too small");
+      int rc = dispatch_plan<T>(p, [&](auto c, auto cta) -> int {
+        rms_bwd_vec<T, decltype(c)::value, decltype(cta)::value>
+            <<<(unsigned)grid, p.threads, 0, st>>>((T*)dx, (float*)workspace, (const T*)dy,
+                                                   (const T*)x, (const T*)weight, rms, rows,
+                                                   (int)cols, row_stride, (int)partial_cols, eps);
+        return launch_status("rms_bwd_vec");
+      });
+      if (rc) return rc;
+      rc = finalize_cols<T>((T*)dweight, (T*)dbias, (const float*)workspace, (int)grid, cols, st);
+      if (rc) return rc;
+      note_kernel("row_vec", 2);
+      return 0;
+    }
+    int launches = 0;
+    if (rows > 0) {
+      rms_bwd_dx_generic<T><<<(unsigned)ceil_div(rows, 4), 128, 0, st>>>(
+          (T*)dx, (const T*)dy, (const T*)x, (const T*)weight, rms, rows, cols, row_stride,
+          col_stride, partial_cols, eps);
+      int rc = launch_status("rms_bwd_dx_generic");
+      if (rc) return rc;
+      ++launches;
+    }
+    norm_bwd_cols_generic<T><<<(unsigned)ceil_div(cols, 128), 128, 0, st>>>(
+        (T*)dweight, (T*)dbias, (const T*)dy, (const T*)x, rms, nullptr, rows, cols, row_stride,
+        col_stride, eps, 1);
+    int rc = launch_status("norm_bwd_cols_generic");
+    if (rc) return rc;
+    note_kernel("row_generic", launches + 1);
+    return 0;
+  });
+}

@@ -1,0 +1,9 @@
+from .attention import Attention
+from .geglu import GEGLU
+from .layer_norm import LayerNorm
+from .linear import Linear
+from .masked_softmax import MaskedSoftmax
+from .rms_norm import RMSNorm
+from .softmax import Softmax
+
+__all__ = ["Attention", "GEGLU", "LayerNorm", "Linear", "MaskedSoftmax", "RMSNorm", "Softmax"]
