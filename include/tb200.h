@@ -178,6 +178,10 @@ const char* tb200_last_kernel(void);
 int tb200_last_launch_count(void);
 /* Kernels launched by this process through the library so far. */
 int64_t tb200_total_launches(void);
+/* Every wait inside the tensor-core kernels is bounded; a wait that gives up records a
+ * non-zero code in a device status word and the kernel still runs to its end. This call
+ * synchronises the device and returns that word (0 = healthy); `reset` != 0 clears it. */
+int tb200_device_status(int reset);
 /* Force the CUDA-core kernels (1) or let the dispatcher choose (0). Used by tests to
  * cross-check the tensor-core kernels against the simple ones. Returns the old value. */
 int tb200_set_force_simt(int on);

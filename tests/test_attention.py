@@ -38,9 +38,9 @@ def test_backward(num_batches, num_heads, y_size, x_size, is_causal, device):
     mask = util.randn(num_batches, num_heads, y_size, y_size, seed=4)
 
     def train(fn, dev, use_mask):
-        i, j, l = (t.to(dev).requires_grad_(True) for t in (q, k, v))
+        i, j, l = (t.detach().clone().to(dev).requires_grad_(True) for t in (q, k, v))
         if use_mask:
-            m = mask.to(dev).requires_grad_(True)
+            m = mask.detach().clone().to(dev).requires_grad_(True)
             fn(i, j, l, attn_mask=m).backward(dy.to(dev))
             return i.grad, j.grad, l.grad, m.grad
         fn(i, j, l, is_causal=is_causal).backward(dy.to(dev))
@@ -64,8 +64,8 @@ def test_broadcast_mask(mask_shape, device):
     mask = mask.masked_fill(drop, float("-inf"))
 
     def train(fn, dev):
-        i, j, l = (t.to(dev).requires_grad_(True) for t in (q, k, v))
-        m = mask.to(dev).requires_grad_(True)
+        i, j, l = (t.detach().clone().to(dev).requires_grad_(True) for t in (q, k, v))
+        m = mask.detach().clone().to(dev).requires_grad_(True)
         y = fn(i, j, l, attn_mask=m)
         y.backward(dy.to(dev))
         return y, i.grad, j.grad, l.grad, m.grad
@@ -98,7 +98,7 @@ def test_half_forward_backward(B, H, S, D, is_causal, masked, dt, device):
         mask = torch.zeros(B, 1, S, S).masked_fill(drop, float("-inf")).to(dt)
 
     def train(fn, dev, up):
-        i, j, l = (t.to(dev).to(up).requires_grad_(True) for t in (q, k, v))
+        i, j, l = (t.detach().clone().to(dev).to(up).requires_grad_(True) for t in (q, k, v))
         if mask is not None:
             y = fn(i, j, l, attn_mask=mask.to(dev).to(up))
         else:
@@ -110,8 +110,7 @@ def test_half_forward_backward(B, H, S, D, is_causal, masked, dt, device):
     want = train(torch_oracle.scaled_dot_product_attention, "cpu", torch.float32)
     for g, w_, name in zip(got, want, ["y", "dq", "dk", "dv"]):
         assert g.dtype == dt
-        err = util.max_abs(g, w_)
-        assert err <= 1e-2 or util.ulp_error(g, w_, dt) <= 2.0, f"{name}: max abs err {err}"
+        util.assert_half_close(g, w_, dt, atol=1e-2, ulps=1.0, what=name)
 
 
 def test_argument_errors(device):

@@ -35,9 +35,9 @@ def test_backward(y_size, x_size, affine, device):
     b = util.randn(x_size, seed=3) if affine == "both" else None
 
     def train(fn, dev):
-        i = x.to(dev).requires_grad_(True)
-        j = None if w is None else w.to(dev).requires_grad_(True)
-        k = None if b is None else b.to(dev).requires_grad_(True)
+        i = x.detach().clone().to(dev).requires_grad_(True)
+        j = None if w is None else w.detach().clone().to(dev).requires_grad_(True)
+        k = None if b is None else b.detach().clone().to(dev).requires_grad_(True)
         fn(i, (x_size,), j, k).backward(dy.to(dev))
         return [t.grad for t in (i, j, k) if t is not None]
 
@@ -52,7 +52,7 @@ def test_multi_dim_normalized_shape(device):
     dy = util.randn(6, 5, 8, 16, seed=8)
 
     def train(fn, dev):
-        i, j, k = (t.to(dev).requires_grad_(True) for t in (x, w, b))
+        i, j, k = (t.detach().clone().to(dev).requires_grad_(True) for t in (x, w, b))
         y = fn(i, (8, 16), j, k)
         y.backward(dy.to(dev))
         return y, i.grad, j.grad, k.grad
@@ -85,4 +85,4 @@ def test_half_precision_values(dt, atol, device):
     want = torch_oracle.layer_norm(x.float(), (2048,), w.float(), b.float())
     got = trident.function.layer_norm(x.to(device), (2048,), w.to(device), b.to(device))
     # one rounding of an fp32 result to the 16-bit type
-    assert util.ulp_error(got, want, dt) <= 1.0 or util.max_abs(got, want) <= atol
+    util.assert_half_close(got, want, dt, atol=1e-6, ulps=0.51, what="y")

@@ -36,9 +36,9 @@ def test_backward(num_batches, m_size, n_size, k_size, with_bias, device):
     dy = util.randn(num_batches, m_size, n_size, seed=4)
 
     def train(fn, dev):
-        i = x.to(dev).requires_grad_(True)
-        j = w.to(dev).requires_grad_(True)
-        k = None if b is None else b.to(dev).requires_grad_(True)
+        i = x.detach().clone().to(dev).requires_grad_(True)
+        j = w.detach().clone().to(dev).requires_grad_(True)
+        k = None if b is None else b.detach().clone().to(dev).requires_grad_(True)
         fn(i, j, k).backward(dy.to(dev))
         return [t.grad for t in (i, j, k) if t is not None]
 
@@ -59,7 +59,7 @@ def test_half_forward_backward(num_batches, m_size, n_size, k_size, dt, device):
     dy = util.randn(num_batches, m_size, n_size, seed=4, dtype=dt, std=n_size ** -0.5)
 
     def train(fn, dev, up):
-        i, j, k = (t.to(dev).to(up).requires_grad_(True) for t in (x, w, b))
+        i, j, k = (t.detach().clone().to(dev).to(up).requires_grad_(True) for t in (x, w, b))
         y = fn(i, j, k)
         y.backward(dy.to(dev).to(up))
         return y, i.grad, j.grad, k.grad
@@ -68,8 +68,7 @@ def test_half_forward_backward(num_batches, m_size, n_size, k_size, dt, device):
     want = train(torch_oracle.linear, "cpu", torch.float32)
     for g, wnt, name in zip(got, want, ["y", "dx", "dw", "db"]):
         assert g.dtype == dt
-        err = util.max_abs(g, wnt)
-        assert err <= 1e-2 or util.ulp_error(g, wnt, dt) <= 1.0, f"{name}: max abs err {err}"
+        util.assert_half_close(g, wnt, dt, atol=1e-2, ulps=1.0, what=name)
 
 
 def test_tensor_core_path_is_taken(device):

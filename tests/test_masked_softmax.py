@@ -39,7 +39,7 @@ def test_backward(y_size, x_size, dim, device):
     mask = build_mask(y_size, x_size, dim, 2)
 
     def train(fn, dev):
-        i = x.to(dev).requires_grad_(True)
+        i = x.detach().clone().to(dev).requires_grad_(True)
         fn(i, mask.to(dev), dim).backward(dy.to(dev))
         return i.grad
 

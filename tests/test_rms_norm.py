@@ -38,9 +38,9 @@ def test_backward(y_size, x_size, p, with_bias, device):
     dy = util.randn(y_size, x_size, seed=4)
 
     def train(fn, dev):
-        i = x.to(dev).requires_grad_(True)
-        j = w.to(dev).requires_grad_(True)
-        k = None if b is None else b.to(dev).requires_grad_(True)
+        i = x.detach().clone().to(dev).requires_grad_(True)
+        j = w.detach().clone().to(dev).requires_grad_(True)
+        k = None if b is None else b.detach().clone().to(dev).requires_grad_(True)
         fn(i, p, j, k).backward(dy.to(dev))
         return [t.grad for t in (i, j, k) if t is not None]
 

@@ -49,3 +49,21 @@ def assert_close(got, want, rtol, atol, what=""):
     assert got.shape == want.shape, f"{what}: shape {tuple(got.shape)} != {tuple(want.shape)}"
     ok = close(got, want, rtol, atol)
     assert ok, f"{what}: max abs err {max_abs(got, want):.3e} (rtol={rtol}, atol={atol})"
+
+
+# Relative size of one unit in the last place of a 16-bit type: an fp32 result rounded once
+# to the type is within half of this of the exact value.
+ULP = {torch.bfloat16: 2.0 ** -7, torch.float16: 2.0 ** -10, torch.float32: 2.0 ** -23}
+
+
+def assert_half_close(got, want, dtype, atol, ulps=1.0, what="", tiny=0.0):
+    """|got - want| <= atol + ulps * ULP[dtype] * |want| (+ tiny for subnormal outputs).
+
+    `want` is the float32 oracle; the ulp term is the rounding of the result to `dtype`,
+    which no kernel that returns `dtype` can avoid.
+    """
+    g, w = got.detach().float().cpu(), want.detach().float().cpu()
+    assert g.shape == w.shape, f"{what}: shape {tuple(g.shape)} != {tuple(w.shape)}"
+    bound = atol + ulps * ULP[dtype] * w.abs() + tiny
+    excess = ((g - w).abs() - bound).max().item()
+    assert excess <= 0, f"{what}: exceeds atol={atol} + {ulps} ulp by {excess:.3e} (max abs err {max_abs(g, w):.3e})"

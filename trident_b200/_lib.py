@@ -30,6 +30,7 @@ SIGNATURES = {
     "tb200_last_launch_count": (c_int, []),
     "tb200_set_force_simt": (c_int, [c_int]),
     "tb200_total_launches": (c_i64, []),
+    "tb200_device_status": (c_int, [c_int]),
     "tb200_layer_norm_fwd": (c_int, [c_ptr] * 6 + [c_i64, c_i64, c_f32, c_int, c_ptr]),
     "tb200_layer_norm_bwd_workspace": (c_size, [c_i64, c_i64]),
     "tb200_layer_norm_bwd": (c_int, [c_ptr] * 9 + [c_size, c_i64, c_i64, c_int, c_ptr]),
@@ -96,6 +97,11 @@ def last_launch_count():
 def total_launches():
     """Kernels launched by the library in this process so far."""
     return load().tb200_total_launches()
+
+
+def device_status(reset=False):
+    """Synchronises and returns the tensor-core kernels' status word (0 = healthy)."""
+    return load().tb200_device_status(1 if reset else 0)
 
 
 def set_force_simt(on):
