@@ -20,6 +20,8 @@ SOURCES = [
     "gemm_simt.cu",
     "gemm_tc.cu",
     "attention_simt.cu",
+    "attention_fwd_tc.cu",
+    "attention_bwd_tc.cu",
 ]
 
 NVCC_FLAGS = [

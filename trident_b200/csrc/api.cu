@@ -262,6 +262,11 @@ extern "C" int tb200_attention_fwd(void* out, float* lse, const void* q, const v
                          out_strides, mask, mask_strides, is_causal, softmax_scale))
     return rc;
   cudaStream_t st = (cudaStream_t)stream;
+  if (!force_simt() && attn_tc_supported(a, dtype, q, k, v, out)) {
+    int rc = launch_attn_fwd_tc(out, lse, q, k, v, mask, a, dtype, st);
+    if (rc == 0) note_kernel("attn_tcgen05", 1);
+    return rc;
+  }
   int rc = launch_attn_fwd_simt(out, lse, q, k, v, mask, a, dtype, st);
   if (rc == 0) note_kernel("attn_simt", 1);
   return rc;
@@ -297,6 +302,19 @@ extern "C" int tb200_attention_bwd(void* dq, void* dk, void* dv, void* dmask, co
   float* delta = (float*)workspace;
   int rc = launch_attn_delta(delta, out, dout, a, dtype, st);
   if (rc) return rc;
+  if (!force_simt() && !dmask && attn_tc_supported(a, dtype, q, k, v, out) && aligned16(dout) &&
+      aligned16(dq) && aligned16(dk) && aligned16(dv)) {
+    const size_t delta_bytes = ((size_t)B * H * S * sizeof(float) + 255) & ~(size_t)255;
+    const size_t need = delta_bytes + (size_t)B * H * S * D * sizeof(float);
+    TB200_REQUIRE(workspace_bytes >= need, TB200_ERR_WORKSPACE,
+                  "attention_bwd: workspace of %zu bytes is smaller than the %zu the tensor-core "
+                  "path needs", workspace_bytes, need);
+    TB200_REQUIRE(aligned16(workspace), TB200_ERR_INVALID, "attention_bwd: workspace must be 16-byte aligned");
+    float* dq_acc = (float*)((char*)workspace + delta_bytes);
+    rc = launch_attn_bwd_tc(dq, dk, dv, dout, q, k, v, lse, delta, dq_acc, mask, a, dtype, st);
+    if (rc == 0) note_kernel("attn_tcgen05", 3);
+    return rc;
+  }
   rc = launch_attn_bwd_simt(dq, dk, dv, dmask, dout, q, k, v, lse, delta, mask, a, dtype, st);
   if (rc == 0) note_kernel("attn_simt", 3);
   return rc;

@@ -31,3 +31,19 @@ int launch_attn_bwd_simt(void* dq, void* dk, void* dv, void* dmask, const void* 
                          cudaStream_t st);
 
 }  // namespace tb200
+
+namespace tb200 {
+// tcgen05 kernels (attention_fwd_tc.cu, attention_bwd_tc.cu): 16-bit operands, head size 64
+// or 128, sequence length a multiple of 128, unit innermost strides, 16-byte aligned rows.
+bool attn_tc_supported(const AttnArgs& a, int dtype, const void* q, const void* k, const void* v,
+                       const void* out);
+int launch_attn_fwd_tc(void* out, float* lse, const void* q, const void* k, const void* v,
+                       const void* mask, const AttnArgs& a, int dtype, cudaStream_t st);
+}  // namespace tb200
+
+namespace tb200 {
+// delta must already hold sum_d out*dout; dq_acc is fp32 scratch of B*H*S*D elements.
+int launch_attn_bwd_tc(void* dq, void* dk, void* dv, const void* dout, const void* q, const void* k,
+                       const void* v, const float* lse, const float* delta, float* dq_acc,
+                       const void* mask, const AttnArgs& a, int dtype, cudaStream_t st);
+}  // namespace tb200

@@ -1,0 +1,490 @@
+// tcgen05 attention forward for 16-bit q/k/v with head size 64 or 128 and a sequence
+// length that is a multiple of 128.
+//
+// A CTA owns two adjacent 128-row query tiles of one (batch, head) and walks the key/value
+// sequence in 128-row tiles. Both score tiles and both output accumulators live in tensor
+// memory (S0, S1: 128 fp32 columns each; O0, O1: D columns each: 512 columns at D = 128),
+// so that the tensor pipe works on one query tile while the softmax warps work on the other:
+//
+//   warp 0      TMA producer: Q0, Q1 once, then a 2-stage ring of K tiles and one of V tiles
+//   warp 1      MMA issuer (one thread):  S_t = Q_t K_j^T  (both operands K-major in smem),
+//               O_t += P_t V_j (P_t read from tensor memory, V_j MN-major in smem)
+//   warp 2      tensor-memory allocation
+//   warps 4-7   softmax of query tile 0, warps 8-11 of query tile 1: one thread per score
+//               row; row maximum and sum need no shuffles. exp2 with the softmax scale and
+//               log2(e) folded in; P is written back over S as packed 16-bit values.
+//
+// The running maximum used for the exponent is only advanced when the true maximum has
+// moved by more than 8 (in log2 units); only then is the accumulator O_t rescaled in tensor
+// memory. The final division by the row sum undoes the stale maximum exactly.
+//
+// Causal tiles above the diagonal are skipped, the diagonal tile is masked per element, and
+// CTAs are ordered longest first. An additive mask is read by the softmax threads (each
+// thread its own row segment) with broadcast strides honoured.
+//
+// log-sum-exp saved for backward: lse = ln(2) * m + ln(l) per query row (natural log).
+#include <mutex>
+#include <type_traits>
+
+#include "attention.cuh"
+#include "common.cuh"
+#include "ptx.cuh"
+
+namespace tb200 {
+namespace {
+
+constexpr int TQ = 128;        // query rows per tile
+constexpr int TK = 128;        // key/value rows per tile
+constexpr int FWD_THREADS = 384;
+constexpr float LOG2E = 1.4426950408889634f;
+constexpr float LN2 = 0.6931471805599453f;
+constexpr float RESCALE_THRESHOLD = 8.f;
+
+struct FwdParams {
+  AttnArgs a;
+  void* out;
+  float* lse;
+  const void* mask;
+  int mask_vec;       // mask rows can be read with 16-byte loads
+  int* status;
+  float scale_log2;   // softmax scale * log2(e)
+  int nq;             // query tiles per (batch, head)
+};
+
+template <typename T>
+__device__ inline uint32_t pack_pair(float a, float b);
+template <>
+__device__ inline uint32_t pack_pair<__nv_bfloat16>(float a, float b) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+template <>
+__device__ inline uint32_t pack_pair<__half>(float a, float b) {
+  __half2 v = __floats2half2_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+__device__ inline void tma_load_4d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int x, int y, int z,
+                                   int w) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], "
+      "[%2];" ::"r"(ptx::smem_u32(smem_dst)),
+      "l"(map), "r"(ptx::smem_u32(bar)), "r"(x), "r"(y), "r"(z), "r"(w)
+      : "memory");
+}
+
+// 32 additive-mask values of one row, pre-multiplied by log2(e).
+template <typename T>
+__device__ inline void load_mask32(float (&mv)[32], const T* row, long long col, long long stride, bool vec) {
+  if (vec) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float f[8];
+      unpack<T>(__ldg(reinterpret_cast<const uint4*>(row + col + j * 8)), f);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) mv[j * 8 + i] = f[i] * LOG2E;
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) mv[i] = Traits<T>::to_f(row[(col + i) * stride]) * LOG2E;
+  }
+}
+
+template <typename T, int D, bool CAUSAL, bool MASKED>
+__global__ void __launch_bounds__(FWD_THREADS, 1)
+    attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                       const __grid_constant__ CUtensorMap map_v, const FwdParams p) {
+  constexpr int TILE_BYTES = 128 * D * 2;
+  constexpr int NBOX = D / 64;
+  constexpr int BOX_BYTES = 128 * 64 * 2;
+  constexpr bool IS_BF16 = std::is_same<T, __nv_bfloat16>::value;
+  constexpr uint32_t IDESC_QK = ptx::make_idesc(IS_BF16, false, false, TQ, TK);
+  constexpr uint32_t IDESC_PV = ptx::make_idesc(IS_BF16, false, true, TQ, D);
+  constexpr uint32_t TMEM_COLS = 512;
+  constexpr uint32_t COL_S = 0, COL_O = 256;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* q_smem = smem;                       // [2][TILE_BYTES]
+  uint8_t* k_smem = smem + 2 * TILE_BYTES;      // [2][TILE_BYTES]
+  uint8_t* v_smem = smem + 4 * TILE_BYTES;      // [2][TILE_BYTES]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 6 * TILE_BYTES);
+  uint64_t* q_full = bars;         // [2]
+  uint64_t* k_full = bars + 2;     // [2]
+  uint64_t* k_empty = bars + 4;    // [2]
+  uint64_t* v_full = bars + 6;     // [2]
+  uint64_t* v_empty = bars + 8;    // [2]
+  uint64_t* s_full = bars + 10;    // [2]  MMA -> softmax: scores ready
+  uint64_t* p_full = bars + 12;    // [2]  softmax -> MMA: probabilities written
+  uint64_t* o_done = bars + 14;    // [2]  MMA -> softmax: P V accumulated
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int pair = (int)gridDim.x - 1 - (int)blockIdx.x;  // longest (causal) work first
+  const int bh = blockIdx.y;
+  const int b = bh / (int)p.a.H, h = bh % (int)p.a.H;
+  const int qt0 = 2 * pair, qt1 = 2 * pair + 1;
+  const bool active1 = qt1 < p.nq;
+  const int nkv = (int)(p.a.S / TK);
+  const int n0 = CAUSAL ? qt0 + 1 : nkv;
+  const int n1 = active1 ? (CAUSAL ? qt1 + 1 : nkv) : 0;
+  const int nmax = n0 > n1 ? n0 : n1;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < 12; ++i) ptx::mbar_init(&bars[i], 1);
+    ptx::mbar_init(&p_full[0], 128);
+    ptx::mbar_init(&p_full[1], 128);
+    ptx::mbar_init(&o_done[0], 1);
+    ptx::mbar_init(&o_done[1], 1);
+    *abort_flag = 0;
+    ptx::fence_barrier_init();
+    ptx::prefetch_tensormap(&map_q);
+    ptx::prefetch_tensormap(&map_k);
+    ptx::prefetch_tensormap(&map_v);
+  }
+  if (warp == 2) {
+    ptx::tmem_alloc(tmem_slot, TMEM_COLS);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0 && lane == 0) {
+    // ---------------------------------------------------------------- producer
+    ptx::mbar_expect_tx(&q_full[0], TILE_BYTES);
+#pragma unroll
+    for (int c = 0; c < NBOX; ++c)
+      tma_load_4d(q_smem + c * BOX_BYTES, &map_q, &q_full[0], c * 64, qt0 * TQ, h, b);
+    if (active1) {
+      ptx::mbar_expect_tx(&q_full[1], TILE_BYTES);
+#pragma unroll
+      for (int c = 0; c < NBOX; ++c)
+        tma_load_4d(q_smem + TILE_BYTES + c * BOX_BYTES, &map_q, &q_full[1], c * 64, qt1 * TQ, h, b);
+    }
+    for (int j = 0; j < nmax; ++j) {
+      const int st = j & 1;
+      const uint32_t ph = (j >> 1) & 1;
+      ptx::mbar_wait(&k_empty[st], ph ^ 1, abort_flag, p.status, 11);
+      ptx::mbar_expect_tx(&k_full[st], TILE_BYTES);
+#pragma unroll
+      for (int c = 0; c < NBOX; ++c)
+        tma_load_4d(k_smem + st * TILE_BYTES + c * BOX_BYTES, &map_k, &k_full[st], c * 64, j * TK, h, b);
+      ptx::mbar_wait(&v_empty[st], ph ^ 1, abort_flag, p.status, 12);
+      ptx::mbar_expect_tx(&v_full[st], TILE_BYTES);
+#pragma unroll
+      for (int c = 0; c < NBOX; ++c)
+        tma_load_4d(v_smem + st * TILE_BYTES + c * BOX_BYTES, &map_v, &v_full[st], c * 64, j * TK, h, b);
+    }
+  } else if (warp == 1 && lane == 0) {
+    // ---------------------------------------------------------------- MMA issuer
+    auto issue_qk = [&](int t, int st) {
+      const uint32_t qa = ptx::smem_u32(q_smem + t * TILE_BYTES);
+      const uint32_t ka = ptx::smem_u32(k_smem + st * TILE_BYTES);
+#pragma unroll
+      for (int ks = 0; ks < D / 16; ++ks) {
+        const uint32_t off = (ks >> 2) * BOX_BYTES + (ks & 3) * 32;
+        ptx::umma_ss(tmem_base + COL_S + t * 128, ptx::make_smem_desc(qa + off, 16, 1024),
+                     ptx::make_smem_desc(ka + off, 16, 1024), IDESC_QK, ks != 0);
+      }
+    };
+    auto issue_pv = [&](int t, int st, bool accumulate) {
+      const uint32_t va = ptx::smem_u32(v_smem + st * TILE_BYTES);
+#pragma unroll
+      for (int ks = 0; ks < TK / 16; ++ks) {
+        ptx::umma_ts(tmem_base + COL_O + t * D, tmem_base + COL_S + t * 128 + ks * 8,
+                     ptx::make_smem_desc(va + ks * 2048, BOX_BYTES, 1024), IDESC_PV, accumulate || ks != 0);
+      }
+    };
+    ptx::mbar_wait(&q_full[0], 0, abort_flag, p.status, 21);
+    if (active1) ptx::mbar_wait(&q_full[1], 0, abort_flag, p.status, 22);
+    ptx::mbar_wait(&k_full[0], 0, abort_flag, p.status, 23);
+    ptx::tc_fence_after();
+    issue_qk(0, 0);
+    ptx::umma_commit(&s_full[0]);
+    if (n1 > 0) {
+      issue_qk(1, 0);
+      ptx::umma_commit(&s_full[1]);
+    }
+    ptx::umma_commit(&k_empty[0]);
+    for (int j = 0; j < nmax; ++j) {
+      const int st = j & 1, nst = (j + 1) & 1;
+      const uint32_t ph = (j >> 1) & 1, nph = ((j + 1) >> 1) & 1;
+      const uint32_t jp = j & 1;
+      bool k_next_ready = false;
+      if (j < n0) {
+        ptx::mbar_wait(&p_full[0], jp, abort_flag, p.status, 24);
+        ptx::mbar_wait(&v_full[st], ph, abort_flag, p.status, 25);
+        ptx::tc_fence_after();
+        issue_pv(0, st, j > 0);
+        ptx::umma_commit(&o_done[0]);
+        if (j >= n1) ptx::umma_commit(&v_empty[st]);
+      }
+      if (j + 1 < n0) {
+        ptx::mbar_wait(&k_full[nst], nph, abort_flag, p.status, 26);
+        k_next_ready = true;
+        ptx::tc_fence_after();
+        issue_qk(0, nst);
+        ptx::umma_commit(&s_full[0]);
+        if (j + 1 >= n1) ptx::umma_commit(&k_empty[nst]);
+      }
+      if (j < n1) {
+        ptx::mbar_wait(&p_full[1], jp, abort_flag, p.status, 27);
+        ptx::mbar_wait(&v_full[st], ph, abort_flag, p.status, 28);
+        ptx::tc_fence_after();
+        issue_pv(1, st, j > 0);
+        ptx::umma_commit(&o_done[1]);
+        ptx::umma_commit(&v_empty[st]);
+      }
+      if (j + 1 < n1) {
+        if (!k_next_ready) ptx::mbar_wait(&k_full[nst], nph, abort_flag, p.status, 29);
+        ptx::tc_fence_after();
+        issue_qk(1, nst);
+        ptx::umma_commit(&s_full[1]);
+        ptx::umma_commit(&k_empty[nst]);
+      }
+    }
+  } else if (warp >= 4) {
+    // ---------------------------------------------------------------- softmax + epilogue
+    const int t = (warp - 4) >> 2;
+    const int quarter = warp & 3;
+    const int n = t == 0 ? n0 : n1;
+    const int qt = t == 0 ? qt0 : qt1;
+    const int row_in_tile = quarter * 32 + lane;
+    const long long row_g = (long long)qt * TQ + row_in_tile;
+    const uint32_t lane_off = static_cast<uint32_t>(quarter * 32) << 16;
+    const uint32_t s_addr = tmem_base + lane_off + COL_S + t * 128;
+    const uint32_t o_addr = tmem_base + lane_off + COL_O + t * D;
+    const T* mask_row = nullptr;
+    if constexpr (MASKED)
+      mask_row = reinterpret_cast<const T*>(p.mask) + (long long)b * p.a.ms[0] + (long long)h * p.a.ms[1] +
+                 row_g * p.a.ms[2];
+    float m_used = -INFINITY, l = 0.f;
+    for (int j = 0; j < n; ++j) {
+      ptx::mbar_wait(&s_full[t], j & 1, abort_flag, p.status, 31);
+      ptx::tc_fence_after();
+      const long long kv0 = (long long)j * TK;
+      const bool diag = CAUSAL && (j == n - 1);
+      // pass 1: row maximum of the scaled (and masked) scores, in log2 units
+      float mx = -INFINITY;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t r[32];
+        ptx::tmem_ld32(s_addr + c * 32, r);
+        ptx::tmem_ld_wait();
+        float mv[32];
+        if constexpr (MASKED) load_mask32<T>(mv, mask_row, kv0 + c * 32, p.a.ms[3], p.mask_vec != 0);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          float s = __uint_as_float(r[i]) * p.scale_log2;
+          if constexpr (MASKED) s += mv[i];
+          if (diag && (kv0 + c * 32 + i > row_g)) s = -INFINITY;
+          mx = fmaxf(mx, s);
+        }
+      }
+      const float m_new = fmaxf(m_used, mx);
+      if (j == 0) {
+        m_used = m_new;
+      } else {
+        const bool need = m_new > m_used + RESCALE_THRESHOLD;
+        if (__any_sync(0xffffffffu, need)) {
+          // the previous P V must have landed before O is touched
+          ptx::mbar_wait(&o_done[t], (j - 1) & 1, abort_flag, p.status, 32);
+          ptx::tc_fence_after();
+          const float factor = m_new == -INFINITY ? 1.f : exp2f(m_used - m_new);
+#pragma unroll 1
+          for (int c = 0; c < D / 32; ++c) {
+            uint32_t r[32];
+            ptx::tmem_ld32(o_addr + c * 32, r);
+            ptx::tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * factor);
+            ptx::tmem_st32(o_addr + c * 32, r);
+          }
+          ptx::tmem_st_wait();
+          l *= factor;
+          m_used = m_new;
+        }
+      }
+      const float m_safe = m_used == -INFINITY ? 0.f : m_used;
+      // pass 2: probabilities, row sum, P written over S as packed 16-bit pairs
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t r[32];
+        ptx::tmem_ld32(s_addr + c * 32, r);
+        ptx::tmem_ld_wait();
+        float mv[32];
+        if constexpr (MASKED) load_mask32<T>(mv, mask_row, kv0 + c * 32, p.a.ms[3], p.mask_vec != 0);
+        uint32_t packed[16];
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          float s0 = fmaf(__uint_as_float(r[i]), p.scale_log2, -m_safe);
+          float s1 = fmaf(__uint_as_float(r[i + 1]), p.scale_log2, -m_safe);
+          if constexpr (MASKED) {
+            s0 += mv[i];
+            s1 += mv[i + 1];
+          }
+          if (diag) {
+            if (kv0 + c * 32 + i > row_g) s0 = -INFINITY;
+            if (kv0 + c * 32 + i + 1 > row_g) s1 = -INFINITY;
+          }
+          const float p0 = exp2f(s0), p1 = exp2f(s1);
+          l += p0 + p1;
+          packed[i >> 1] = pack_pair<T>(p0, p1);
+        }
+        ptx::tmem_st16(s_addr + c * 16, packed);
+      }
+      ptx::tmem_st_wait();
+      ptx::tc_fence_before();
+      ptx::mbar_arrive(&p_full[t]);
+    }
+    if (n > 0) {
+      ptx::mbar_wait(&o_done[t], (n - 1) & 1, abort_flag, p.status, 33);
+      ptx::tc_fence_after();
+      const float inv = 1.f / l;
+      T* orow = reinterpret_cast<T*>(p.out) + (long long)b * p.a.os[0] + (long long)h * p.a.os[1] +
+                row_g * p.a.os[2];
+#pragma unroll 1
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t r[32];
+        ptx::tmem_ld32(o_addr + c * 32, r);
+        ptx::tmem_ld_wait();
+#pragma unroll
+        for (int jv = 0; jv < 4; ++jv) {
+          uint4 o;
+          o.x = pack_pair<T>(__uint_as_float(r[jv * 8 + 0]) * inv, __uint_as_float(r[jv * 8 + 1]) * inv);
+          o.y = pack_pair<T>(__uint_as_float(r[jv * 8 + 2]) * inv, __uint_as_float(r[jv * 8 + 3]) * inv);
+          o.z = pack_pair<T>(__uint_as_float(r[jv * 8 + 4]) * inv, __uint_as_float(r[jv * 8 + 5]) * inv);
+          o.w = pack_pair<T>(__uint_as_float(r[jv * 8 + 6]) * inv, __uint_as_float(r[jv * 8 + 7]) * inv);
+          *reinterpret_cast<uint4*>(orow + c * 32 + jv * 8) = o;
+        }
+      }
+      const float m_safe = m_used == -INFINITY ? 0.f : m_used;
+      p.lse[((long long)b * p.a.H + h) * p.a.S + row_g] = m_safe * LN2 + logf(l);
+    }
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  if (warp == 2) {
+    ptx::tc_fence_after();
+    ptx::tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                              const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                              CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeFn encode_fn4() {
+  static EncodeFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeFn>(sym);
+    else
+      cudaGetLastError();
+  });
+  return fn;
+}
+
+}  // namespace
+
+// 4-D tensor map over a [B,H,S,D] 16-bit tensor with element strides st[0..3] (st[3] == 1),
+// box [1,1,box_rows,64], 128-byte swizzle.
+bool make_tensor_map_bhsd(CUtensorMap* map, const void* base, int64_t B, int64_t H, int64_t S, int64_t D,
+                          const int64_t* st, uint32_t box_rows) {
+  EncodeFn fn = encode_fn4();
+  if (!fn) {
+    set_error("cuTensorMapEncodeTiled is not available from the driver");
+    return false;
+  }
+  // a dimension of extent 1 may carry any stride in torch; give it a well-formed one
+  int64_t ss = st[2], sh = st[1], sb = st[0];
+  if (S == 1) ss = D;
+  if (H == 1) sh = ss * S;
+  if (B == 1) sb = sh * H;
+  cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)S, (cuuint64_t)H, (cuuint64_t)B};
+  cuuint64_t strides[3] = {(cuuint64_t)ss * 2, (cuuint64_t)sh * 2, (cuuint64_t)sb * 2};
+  cuuint32_t box[4] = {64, box_rows, 1, 1};
+  cuuint32_t elem[4] = {1, 1, 1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT16, 4, const_cast<void*>(base), dims, strides, box, elem,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_error("cuTensorMapEncodeTiled (4-D) failed with CUresult %d", (int)r);
+    return false;
+  }
+  return true;
+}
+
+static bool strides_ok(const void* ptr, const int64_t* st, int64_t B, int64_t H, int64_t S) {
+  if (!aligned16(ptr) || st[3] != 1) return false;
+  if (S > 1 && (st[2] % 8 || st[2] <= 0)) return false;
+  if (H > 1 && (st[1] % 8 || st[1] <= 0)) return false;
+  if (B > 1 && (st[0] % 8 || st[0] <= 0)) return false;
+  return true;
+}
+
+bool attn_tc_supported(const AttnArgs& a, int dtype, const void* q, const void* k, const void* v,
+                       const void* out) {
+  if (dtype != TB200_F16 && dtype != TB200_BF16) return false;
+  if (a.D != 64 && a.D != 128) return false;
+  if (a.S % 128 != 0 || a.S <= 0) return false;
+  if (a.B * a.H > 65535 || a.S >= (1ll << 30)) return false;
+  if (!strides_ok(q, a.qs, a.B, a.H, a.S) || !strides_ok(k, a.ks, a.B, a.H, a.S) ||
+      !strides_ok(v, a.vs, a.B, a.H, a.S) || !strides_ok(out, a.os, a.B, a.H, a.S))
+    return false;
+  return encode_fn4() != nullptr;
+}
+
+template <typename T, int D, bool CAUSAL, bool MASKED>
+static int launch_fwd(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const FwdParams& p,
+                      cudaStream_t st) {
+  constexpr int SMEM = 6 * 128 * D * 2 + 1024 + 256;
+  auto kern = attn_fwd_tc_kernel<T, D, CAUSAL, MASKED>;
+  static std::once_flag once;
+  static cudaError_t attr_err = cudaSuccess;
+  std::call_once(once, [&] { attr_err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM); });
+  if (attr_err != cudaSuccess) {
+    set_error("attention_fwd: cudaFuncSetAttribute failed: %s", cudaGetErrorString(attr_err));
+    return (int)attr_err;
+  }
+  dim3 grid((unsigned)((p.nq + 1) / 2), (unsigned)(p.a.B * p.a.H));
+  kern<<<grid, FWD_THREADS, SMEM, st>>>(mq, mk, mv, p);
+  return launch_status("attn_fwd_tc");
+}
+
+int launch_attn_fwd_tc(void* out, float* lse, const void* q, const void* k, const void* v, const void* mask,
+                       const AttnArgs& a, int dtype, cudaStream_t st) {
+  CUtensorMap mq, mk, mv;
+  if (!make_tensor_map_bhsd(&mq, q, a.B, a.H, a.S, a.D, a.qs, 128) ||
+      !make_tensor_map_bhsd(&mk, k, a.B, a.H, a.S, a.D, a.ks, 128) ||
+      !make_tensor_map_bhsd(&mv, v, a.B, a.H, a.S, a.D, a.vs, 128))
+    return TB200_ERR_UNSUPPORTED;
+  FwdParams p;
+  p.a = a;
+  p.out = out;
+  p.lse = lse;
+  p.mask = mask;
+  p.mask_vec = mask && a.ms[3] == 1 && aligned16(mask) && a.ms[2] % 8 == 0 && a.ms[1] % 8 == 0 && a.ms[0] % 8 == 0;
+  p.status = device_status_ptr();
+  p.scale_log2 = a.scale * LOG2E;
+  p.nq = (int)(a.S / TQ);
+  auto go = [&](auto tag, auto dsel) -> int {
+    using T = decltype(tag);
+    constexpr int D = decltype(dsel)::value;
+    if (a.causal) return launch_fwd<T, D, true, false>(mq, mk, mv, p, st);
+    if (mask) return launch_fwd<T, D, false, true>(mq, mk, mv, p, st);
+    return launch_fwd<T, D, false, false>(mq, mk, mv, p, st);
+  };
+  if (dtype == TB200_BF16)
+    return a.D == 128 ? go(__nv_bfloat16{}, IntD<128>{}) : go(__nv_bfloat16{}, IntD<64>{});
+  return a.D == 128 ? go(__half{}, IntD<128>{}) : go(__half{}, IntD<64>{});
+}
+
+}  // namespace tb200
