@@ -58,6 +58,26 @@ int tb200_layer_norm_bwd(void* dx, void* dweight /*nullable*/, void* dbias /*nul
                          size_t workspace_bytes, int64_t rows, int64_t cols, int dtype,
                          void* stream);
 
+/* Same result as tb200_layer_norm_bwd, but the caller passes no workspace and nothing is
+ * allocated: the column partials of dweight/dbias go to a 2 MiB array that is part of the
+ * library image on every GPU that loads it. It exists for callers that cannot allocate
+ * device memory at the point of the call: a process that gave its whole GPU to a private
+ * arena at start-up, or code under a no-cudaMalloc rule on its request path. (It has no
+ * counterpart in the reference, whose operation layer always allocates its staging
+ * buffers with torch.)
+ *   - cols may be at most 8192; wider rows are rejected with TB200_ERR_UNSUPPORTED and
+ *     should use tb200_layer_norm_bwd with a workspace;
+ *   - the first call on each device resolves the array's device address (the device must
+ *     be current); make that first call before any stream capture begins;
+ *   - all calls on one device share the array: two calls that may run on the GPU at the
+ *     same time (different streams) race on it and must be serialised by the caller.
+ *     Nothing in the array has to be cleared between calls; each call overwrites every
+ *     element it later reads. */
+int tb200_layer_norm_bwd_static(void* dx, void* dweight /*nullable*/, void* dbias /*nullable*/,
+                                const void* dy, const void* x, const void* weight /*nullable*/,
+                                const float* mean, const float* rstd, int64_t rows, int64_t cols,
+                                int dtype, void* stream);
+
 /* ---- RMSNorm ------------------------------------------------------------
  * Replaces kernel.RMSNorm.forward (trident/kernel/rms_norm.py:19-117), launched at
  * trident/operation/rms_norm.py:60. rms = sqrt(mean(x[:partial_cols]^2));

@@ -34,6 +34,7 @@ SIGNATURES = {
     "tb200_layer_norm_fwd": (c_int, [c_ptr] * 6 + [c_i64, c_i64, c_f32, c_int, c_ptr]),
     "tb200_layer_norm_bwd_workspace": (c_size, [c_i64, c_i64]),
     "tb200_layer_norm_bwd": (c_int, [c_ptr] * 9 + [c_size, c_i64, c_i64, c_int, c_ptr]),
+    "tb200_layer_norm_bwd_static": (c_int, [c_ptr] * 8 + [c_i64, c_i64, c_int, c_ptr]),
     "tb200_rms_norm_fwd": (c_int, [c_ptr] * 5 + [c_i64] * 5 + [c_f32, c_int, c_ptr]),
     "tb200_rms_norm_bwd_workspace": (c_size, [c_i64, c_i64]),
     "tb200_rms_norm_bwd": (c_int, [c_ptr] * 8 + [c_size] + [c_i64] * 5 + [c_f32, c_int, c_ptr]),
@@ -164,6 +165,20 @@ def layer_norm_bwd(dx, dweight, dbias, dy, x, weight, mean, rstd, workspace, row
             rows, cols, dtype_code(x.dtype), _stream(x),
         ),
         "tb200_layer_norm_bwd",
+    )
+
+
+def layer_norm_bwd_static(dx, dweight, dbias, dy, x, weight, mean, rstd, rows, cols):
+    """LayerNorm backward for callers that cannot allocate device memory: same outputs as
+    layer_norm_bwd, no workspace argument (the library's built-in 2 MiB scratch is used;
+    cols <= 8192; calls on one device must not overlap on the GPU)."""
+    _require_cuda(dx, dy, x)
+    _check(
+        load().tb200_layer_norm_bwd_static(
+            _ptr(dx), _ptr(dweight), _ptr(dbias), _ptr(dy), _ptr(x), _ptr(weight),
+            _ptr(mean), _ptr(rstd), rows, cols, dtype_code(x.dtype), _stream(x),
+        ),
+        "tb200_layer_norm_bwd_static",
     )
 
 

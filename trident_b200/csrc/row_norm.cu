@@ -562,3 +562,114 @@ extern "C" int tb200_rms_norm_bwd(void* dx, void* dweight, void* dbias, const vo
     return 0;
   });
 }
+
+// ---------------------------------------------------------------------------
+// LayerNorm backward without any caller-provided or allocated scratch.
+//
+// The regular entry point above needs a workspace for the per-CTA column partials of the
+// weight and bias gradients, which the caller sizes with a query and allocates. Some callers
+// cannot do that: a server that handed every byte of device memory to its own arena at
+// start-up has nothing left to allocate from, and a caller bound to a "no cudaMalloc on the
+// request path" rule (cudaMalloc stalls the whole device) may not allocate at all. For them
+// the partials live in the fixed array below, which every GPU that loads the library holds
+// from load to exit.
+// ---------------------------------------------------------------------------
+#include <mutex>
+
+namespace tb200 {
+
+constexpr size_t LN_STATIC_SCRATCH_FLOATS = 512 * 1024;  // 2 MiB per device
+constexpr int64_t LN_STATIC_MAX_COLS = 8192;             // leaves room for at least 32 partial rows
+
+static __device__ __align__(256) float g_ln_bwd_scratch[LN_STATIC_SCRATCH_FLOATS];
+
+// Device address of the array above on the current device. In host code the array's name is
+// only a handle, not an address a kernel could use, so it is resolved once per device (with
+// that device current) and remembered.
+static int ln_static_scratch(float** out) {
+  static std::mutex mu;
+  static float* resolved[64] = {nullptr};
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= 64) {
+    set_error("layer_norm_bwd_static: no current CUDA device (%s)", cudaGetErrorString(e));
+    return e != cudaSuccess ? (int)e : TB200_ERR_UNSUPPORTED;
+  }
+  std::lock_guard<std::mutex> lock(mu);
+  if (resolved[dev] == nullptr) {
+    float* p = nullptr;
+    e = cudaGetSymbolAddress((void**)&p, g_ln_bwd_scratch);
+    if (e != cudaSuccess || p == nullptr) {
+      set_error("layer_norm_bwd_static: cudaGetSymbolAddress failed on device %d: %s", dev,
+                cudaGetErrorString(e));
+      return e != cudaSuccess ? (int)e : TB200_ERR_UNSUPPORTED;
+    }
+    resolved[dev] = p;
+  }
+  *out = resolved[dev];
+  return 0;
+}
+
+}  // namespace tb200
+
+extern "C" int tb200_layer_norm_bwd_static(void* dx, void* dweight, void* dbias, const void* dy,
+                                           const void* x, const void* weight, const float* mean,
+                                           const float* rstd, int64_t rows, int64_t cols, int dtype,
+                                           void* stream) {
+  TB200_REQUIRE(dx && dy && x && mean && rstd, TB200_ERR_INVALID,
+                "layer_norm_bwd_static: null pointer");
+  TB200_REQUIRE(rows >= 0 && cols > 0, TB200_ERR_INVALID, "layer_norm_bwd_static: bad shape");
+  TB200_REQUIRE(cols <= LN_STATIC_MAX_COLS, TB200_ERR_UNSUPPORTED,
+                "layer_norm_bwd_static: %lld columns exceed the built-in scratch (at most %lld); use "
+                "tb200_layer_norm_bwd with a workspace",
+                (long long)cols, (long long)LN_STATIC_MAX_COLS);
+  cudaStream_t st = (cudaStream_t)stream;
+  const bool want_cols = dweight || dbias;
+  float* scratch = nullptr;
+  if (want_cols) {
+    if (int rc = ln_static_scratch(&scratch)) return rc;
+  }
+  return dispatch_dtype(dtype, [&](auto tag) -> int {
+    using T = decltype(tag);
+    const bool ok = aligned16(dx) && aligned16(dy) && aligned16(x) && (!weight || aligned16(weight));
+    RowPlan p = plan_rows<T>(cols, ok, max_chunks<T>() / 2);
+    if (p.vec && rows > 0) {
+      int64_t grid = persistent_grid(p, rows);
+      const int64_t fit = (int64_t)(LN_STATIC_SCRATCH_FLOATS / (size_t)(2 * cols));
+      if (grid > fit) grid = fit;  // fewer, longer-running CTAs: one [2, cols] partial row each
+      int rc = dispatch_plan<T>(p, [&](auto c, auto cta) -> int {
+        ln_bwd_vec<T, decltype(c)::value, decltype(cta)::value>
+            <<<(unsigned)grid, p.threads, 0, st>>>((T*)dx, scratch, (const T*)dy, (const T*)x,
+                                                   (const T*)weight, mean, rstd, rows, (int)cols,
+                                                   want_cols ? 1 : 0);
+        return launch_status("ln_bwd_vec (static scratch)");
+      });
+      if (rc) return rc;
+      if (want_cols) {
+        rc = finalize_cols<T>((T*)dweight, (T*)dbias, scratch, (int)grid, cols, st);
+        if (rc) return rc;
+      }
+      note_kernel("row_vec", want_cols ? 2 : 1);
+      return 0;
+    }
+    // widths the vector kernel does not take need no scratch at all
+    int launches = 0;
+    if (rows > 0) {
+      ln_bwd_dx_generic<T><<<(unsigned)ceil_div(rows, 4), 128, 0, st>>>(
+          (T*)dx, (const T*)dy, (const T*)x, (const T*)weight, mean, rstd, rows, cols);
+      int rc = launch_status("ln_bwd_dx_generic");
+      if (rc) return rc;
+      ++launches;
+    }
+    if (want_cols) {
+      norm_bwd_cols_generic<T><<<(unsigned)ceil_div(cols, 128), 128, 0, st>>>(
+          (T*)dweight, (T*)dbias, (const T*)dy, (const T*)x, mean, rstd, rows, cols, cols, 1, 0.f,
+          0);
+      int rc = launch_status("norm_bwd_cols_generic");
+      if (rc) return rc;
+      ++launches;
+    }
+    note_kernel("row_generic", launches);
+    return 0;
+  });
+}
