@@ -37,7 +37,7 @@ if ROOT not in sys.path:
 
 import torch  # noqa: E402
 
-DEFAULT_WORKLOAD = "softmax"
+DEFAULT_WORKLOAD = "attention_causal"
 L2_BYTES = 126 * 1024 * 1024
 
 # Bounded CPU samples: keyword arguments of Workload.make that shrink the sharded dimension.
@@ -370,11 +370,12 @@ def run_reference(args, wl):
 
 
 def measure(wl, args, rank, world, device, with_cpu, sampler=None):
-    from trident_b200.workloads import owned_blocks
+    from trident_b200.workloads import set_replica
 
     pk = peaks()
-    kw = {}
-    tensors = wl.make(rank, world, device, **kw)
+    kw = {"scale": args.scale} if args.scale > 1 else {}
+    set_replica(rank)  # weak scaling: every rank runs one full-size replica of the configuration
+    tensors = wl.make(0, 1, device, **kw)
     work_local = wl.work(tensors)
     nbytes = set_bytes(wl, tensors)
     nsets = 1 if nbytes >= 2 * L2_BYTES else min(8, -(-3 * L2_BYTES // max(nbytes, 1)))
@@ -398,10 +399,11 @@ def measure(wl, args, rank, world, device, with_cpu, sampler=None):
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": secs / args.steps * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": str(wl.dtype).replace("torch.", ""), "data": "synthetic",
-        "config": {"workload": wl.describe, "baseline_config": wl.config_index, "launch": mode,
+        "config": {"workload": wl.describe + ("" if args.scale == 1 else f" [sharded dimension / {args.scale}]"),
+                   "baseline_config": wl.config_index, "launch": mode,
                    "l2": (f"rotating {nsets} input sets ({nsets * nbytes / 2**20:.0f} MiB)" if nsets > 1
                           else f"inputs {nbytes / 2**20:.0f} MiB exceed L2"),
-                   "shard": f"rank {rank} owns blocks {list(owned_blocks(rank, world))} of 8"},
+                   "shard": f"each of {world} rank(s) runs one full-size replica (replica = rank)"},
         "step_frac_of_peak": value / (peak * world),
         "roofline": {"bound": wl.bound, "kernel": label, "achieved": achieved, "peak": peak,
                      "unit": unit_of(wl), "frac": achieved / peak, "traffic": None,
@@ -427,6 +429,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD)
+    ap.add_argument("--scale", type=int, default=1,
+                    help="divide the sharded dimension (rows, batch x heads) by this: small cases for profiling")
     ap.add_argument("--others", default="auto",
                     help="comma list of further workloads reported under 'workloads' (auto: all at N=1, none "
                          "otherwise; 'none' to skip)")

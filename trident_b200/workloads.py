@@ -28,9 +28,19 @@ def owned_blocks(rank: int, world: int) -> range:
     return range(rank * per, (rank + 1) * per)
 
 
+_REPLICA = 0
+
+
+def set_replica(replica: int) -> None:
+    """Selects which independent replica of the data `make` generates (weak scaling: rank r
+    of a multi-GPU benchmark run works on replica r of the full configuration)."""
+    global _REPLICA
+    _REPLICA = int(replica)
+
+
 def _gen(seed: int, block: int, device) -> torch.Generator:
     g = torch.Generator(device=device)
-    g.manual_seed(seed * 1000003 + block)
+    g.manual_seed(seed * 1000003 + 10007 * _REPLICA + block)
     return g
 
 
@@ -181,6 +191,12 @@ def _attn_make(rank, world, device, scale, B, H, S, D, seed, masked):
     out = {"q": torch.cat(qs), "k": torch.cat(ks), "v": torch.cat(vs), "dy": torch.cat(gs)}
     if masked:
         out["mask"] = torch.cat(ms)
+    else:
+        # the (batch, head) units are independent: present them with the configuration's head
+        # count when they divide evenly ([4, 32, S, D] for the full causal configuration)
+        units = out["q"].shape[0] * out["q"].shape[1]
+        if units % H == 0:
+            out = {name: t.reshape(units // H, H, S, D) for name, t in out.items()}
     return out
 
 
