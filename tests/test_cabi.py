@@ -86,6 +86,6 @@ def test_workspace_queries():
     assert lib.tb200_rms_norm_bwd_workspace(8192, 4096) >= 148 * 2 * 4096 * 4
     assert lib.tb200_linear_bwd_bias_workspace(8192, 22016) >= 22016 * 4
     assert lib.tb200_linear_bwd_bias_workspace(0, 16) == 0
-    # fp32 delta [B,H,S] plus, for 16-bit inputs, an fp32 dq accumulator [B,H,S,D]
-    assert lib.tb200_attention_bwd_workspace(2, 3, 128, 64, 0) == 2 * 3 * 128 * 4
-    assert lib.tb200_attention_bwd_workspace(2, 3, 128, 64, 2) == 2 * 3 * 128 * 4 + 2 * 3 * 128 * 64 * 4
+    # two fp32 row arrays [B,H,S] plus, for 16-bit inputs, an fp32 dq accumulator [B,H,S,D]
+    assert lib.tb200_attention_bwd_workspace(2, 3, 128, 64, 0) == 2 * 2 * 3 * 128 * 4
+    assert lib.tb200_attention_bwd_workspace(2, 3, 128, 64, 2) == 2 * 2 * 3 * 128 * 4 + 2 * 3 * 128 * 64 * 4

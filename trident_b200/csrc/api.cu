@@ -272,13 +272,18 @@ extern "C" int tb200_attention_fwd(void* out, float* lse, const void* q, const v
   return rc;
 }
 
+// Row scratch of the backward pass: two float arrays of B*H*S elements (the CUDA-core path
+// uses the first as delta; the tensor-core path stores -delta and -lse*log2e), 256-byte
+// aligned, followed for 16-bit inputs by the fp32 dq accumulator [B,H,S,D].
+static size_t attn_row_scratch_bytes(int64_t B, int64_t H, int64_t S) {
+  return ((size_t)2 * B * H * S * sizeof(float) + 255) & ~(size_t)255;
+}
+
 extern "C" size_t tb200_attention_bwd_workspace(int64_t B, int64_t H, int64_t S, int64_t D,
                                                 int dtype) {
   if (B <= 0 || H <= 0 || S <= 0 || D <= 0) return 0;
-  size_t delta = (size_t)B * H * S * sizeof(float);
-  delta = (delta + 255) & ~(size_t)255;
-  size_t dq_acc = dtype == TB200_F32 ? 0 : (size_t)B * H * S * D * sizeof(float);
-  return delta + dq_acc;
+  const size_t dq_acc = dtype == TB200_F32 ? 0 : (size_t)B * H * S * D * sizeof(float);
+  return attn_row_scratch_bytes(B, H, S) + dq_acc;
 }
 
 extern "C" int tb200_attention_bwd(void* dq, void* dk, void* dv, void* dmask, const void* dout,
@@ -299,22 +304,23 @@ extern "C" int tb200_attention_bwd(void* dq, void* dk, void* dv, void* dmask, co
   TB200_REQUIRE(workspace_bytes >= (size_t)B * H * S * sizeof(float), TB200_ERR_WORKSPACE,
                 "attention_bwd: workspace too small");
   cudaStream_t st = (cudaStream_t)stream;
-  float* delta = (float*)workspace;
-  int rc = launch_attn_delta(delta, out, dout, a, dtype, st);
-  if (rc) return rc;
   if (!force_simt() && !dmask && attn_tc_supported(a, dtype, q, k, v, out) && aligned16(dout) &&
       aligned16(dq) && aligned16(dk) && aligned16(dv)) {
-    const size_t delta_bytes = ((size_t)B * H * S * sizeof(float) + 255) & ~(size_t)255;
-    const size_t need = delta_bytes + (size_t)B * H * S * D * sizeof(float);
+    const size_t row_bytes = attn_row_scratch_bytes(B, H, S);
+    const size_t need = row_bytes + (size_t)B * H * S * D * sizeof(float);
     TB200_REQUIRE(workspace_bytes >= need, TB200_ERR_WORKSPACE,
                   "attention_bwd: workspace of %zu bytes is smaller than the %zu the tensor-core "
                   "path needs", workspace_bytes, need);
     TB200_REQUIRE(aligned16(workspace), TB200_ERR_INVALID, "attention_bwd: workspace must be 16-byte aligned");
-    float* dq_acc = (float*)((char*)workspace + delta_bytes);
-    rc = launch_attn_bwd_tc(dq, dk, dv, dout, q, k, v, lse, delta, dq_acc, mask, a, dtype, st);
+    float* dq_acc = (float*)((char*)workspace + row_bytes);
+    int rc = launch_attn_bwd_tc(dq, dk, dv, dout, q, k, v, out, lse, (float*)workspace, dq_acc, mask, a,
+                                dtype, st);
     if (rc == 0) note_kernel("attn_tcgen05", 3);
     return rc;
   }
+  float* delta = (float*)workspace;
+  int rc = launch_attn_delta(delta, out, dout, a, dtype, st);
+  if (rc) return rc;
   rc = launch_attn_bwd_simt(dq, dk, dv, dmask, dout, q, k, v, lse, delta, mask, a, dtype, st);
   if (rc == 0) note_kernel("attn_simt", 3);
   return rc;

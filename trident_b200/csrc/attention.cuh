@@ -42,8 +42,9 @@ int launch_attn_fwd_tc(void* out, float* lse, const void* q, const void* k, cons
 }  // namespace tb200
 
 namespace tb200 {
-// delta must already hold sum_d out*dout; dq_acc is fp32 scratch of B*H*S*D elements.
+// row_scratch: 2 * B*H*S floats (-delta and -lse*log2e, written by a first small kernel);
+// dq_acc: fp32 scratch of B*H*S*D elements.
 int launch_attn_bwd_tc(void* dq, void* dk, void* dv, const void* dout, const void* q, const void* k,
-                       const void* v, const float* lse, const float* delta, float* dq_acc,
-                       const void* mask, const AttnArgs& a, int dtype, cudaStream_t st);
+                       const void* v, const void* out, const float* lse, float* row_scratch,
+                       float* dq_acc, const void* mask, const AttnArgs& a, int dtype, cudaStream_t st);
 }  // namespace tb200

@@ -27,13 +27,14 @@
 #include <type_traits>
 
 #include "attention.cuh"
+#include "attn_math.cuh"
 #include "common.cuh"
 #include "ptx.cuh"
 
 namespace tb200 {
 namespace {
 
-constexpr int TQ = 128;        // query rows per tile
+constexpr int TQ = 128;       // query rows per tile
 constexpr int TK = 128;        // key/value rows per tile
 constexpr int FWD_THREADS = 384;
 constexpr float LOG2E = 1.4426950408889634f;
@@ -269,19 +270,48 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
       const bool diag = CAUSAL && (j == n - 1);
       // pass 1: row maximum of the scaled (and masked) scores, in log2 units
       float mx = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t r[32];
-        ptx::tmem_ld32(s_addr + c * 32, r);
-        ptx::tmem_ld_wait();
-        float mv[32];
-        if constexpr (MASKED) load_mask32<T>(mv, mask_row, kv0 + c * 32, p.a.ms[3], p.mask_vec != 0);
+      const bool plain = !MASKED && !diag;  // uniform over the CTA's softmax warps of this tile
+      if (plain) {
+        // raw maximum (the scale is positive), two elements per three-input max, the load of
+        // the next 32 columns in flight while the current ones are reduced
+        uint32_t ra[32], rb[32];
+        float m0 = -INFINITY, m1 = -INFINITY;
+        auto reduce32 = [&](const uint32_t (&r)[32]) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float s = __uint_as_float(r[i]) * p.scale_log2;
-          if constexpr (MASKED) s += mv[i];
-          if (diag && (kv0 + c * 32 + i > row_g)) s = -INFINITY;
-          mx = fmaxf(mx, s);
+          for (int i = 0; i < 32; i += 4) {
+            m0 = am::max3(m0, __uint_as_float(r[i]), __uint_as_float(r[i + 1]));
+            m1 = am::max3(m1, __uint_as_float(r[i + 2]), __uint_as_float(r[i + 3]));
+          }
+        };
+        ptx::tmem_ld32(s_addr, ra);
+        am::tmem_ld_wait_dep(ra);
+        ptx::tmem_ld32(s_addr + 32, rb);
+        reduce32(ra);
+        am::tmem_ld_wait_dep(rb);
+        ptx::tmem_ld32(s_addr + 64, ra);
+        reduce32(rb);
+        am::tmem_ld_wait_dep(ra);
+        ptx::tmem_ld32(s_addr + 96, rb);
+        reduce32(ra);
+        am::tmem_ld_wait_dep(rb);
+        reduce32(rb);
+        mx = fmaxf(m0, m1) * p.scale_log2;
+      } else {
+        const int lim = CAUSAL ? row_in_tile : 1 << 30;  // columns above `lim` are masked (diagonal tile)
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          uint32_t r[32];
+          ptx::tmem_ld32(s_addr + c * 32, r);
+          ptx::tmem_ld_wait();
+          float mv[32];
+          if constexpr (MASKED) load_mask32<T>(mv, mask_row, kv0 + c * 32, p.a.ms[3], p.mask_vec != 0);
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            float s = __uint_as_float(r[i]) * p.scale_log2;
+            if constexpr (MASKED) s += mv[i];
+            if (c * 32 + i > lim) s = -INFINITY;
+            mx = fmaxf(mx, s);
+          }
         }
       }
       const float m_new = fmaxf(m_used, mx);
@@ -310,31 +340,64 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
       }
       const float m_safe = m_used == -INFINITY ? 0.f : m_used;
       // pass 2: probabilities, row sum, P written over S as packed 16-bit pairs
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t r[32];
-        ptx::tmem_ld32(s_addr + c * 32, r);
-        ptx::tmem_ld_wait();
-        float mv[32];
-        if constexpr (MASKED) load_mask32<T>(mv, mask_row, kv0 + c * 32, p.a.ms[3], p.mask_vec != 0);
-        uint32_t packed[16];
+      if (plain) {
+        const uint64_t scale2 = am::pack2f(p.scale_log2, p.scale_log2);
+        const uint64_t negm2 = am::pack2f(-m_safe, -m_safe);
+        uint64_t lsum = am::pack2f(0.f, 0.f);
+        uint32_t ra[32], rb[32];
+        auto exp32 = [&](const uint32_t (&r)[32], int c) {
+          uint32_t packed[16];
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          float s0 = fmaf(__uint_as_float(r[i]), p.scale_log2, -m_safe);
-          float s1 = fmaf(__uint_as_float(r[i + 1]), p.scale_log2, -m_safe);
-          if constexpr (MASKED) {
-            s0 += mv[i];
-            s1 += mv[i + 1];
+          for (int i = 0; i < 32; i += 2) {
+            float x0, x1;
+            am::unpack2f(am::fma2(am::pack2u(r[i], r[i + 1]), scale2, negm2), x0, x1);
+            const float p0 = am::ex2(x0), p1 = am::ex2(x1);
+            lsum = am::add2(lsum, am::pack2f(p0, p1));
+            packed[i >> 1] = am::cvt_pair<T>(p0, p1);
           }
-          if (diag) {
-            if (kv0 + c * 32 + i > row_g) s0 = -INFINITY;
-            if (kv0 + c * 32 + i + 1 > row_g) s1 = -INFINITY;
+          ptx::tmem_st16(s_addr + c * 16, packed);
+        };
+        ptx::tmem_ld32(s_addr, ra);
+        am::tmem_ld_wait_dep(ra);
+        ptx::tmem_ld32(s_addr + 32, rb);
+        exp32(ra, 0);
+        am::tmem_ld_wait_dep(rb);
+        ptx::tmem_ld32(s_addr + 64, ra);
+        exp32(rb, 1);
+        am::tmem_ld_wait_dep(ra);
+        ptx::tmem_ld32(s_addr + 96, rb);
+        exp32(ra, 2);
+        am::tmem_ld_wait_dep(rb);
+        exp32(rb, 3);
+        float l0, l1;
+        am::unpack2f(lsum, l0, l1);
+        l += l0 + l1;
+      } else {
+        const int lim = CAUSAL ? row_in_tile : 1 << 30;
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          uint32_t r[32];
+          ptx::tmem_ld32(s_addr + c * 32, r);
+          ptx::tmem_ld_wait();
+          float mv[32];
+          if constexpr (MASKED) load_mask32<T>(mv, mask_row, kv0 + c * 32, p.a.ms[3], p.mask_vec != 0);
+          uint32_t packed[16];
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            float s0 = fmaf(__uint_as_float(r[i]), p.scale_log2, -m_safe);
+            float s1 = fmaf(__uint_as_float(r[i + 1]), p.scale_log2, -m_safe);
+            if constexpr (MASKED) {
+              s0 += mv[i];
+              s1 += mv[i + 1];
+            }
+            if (c * 32 + i > lim) s0 = -INFINITY;
+            if (c * 32 + i + 1 > lim) s1 = -INFINITY;
+            const float p0 = am::ex2(s0), p1 = am::ex2(s1);
+            l += p0 + p1;
+            packed[i >> 1] = am::cvt_pair<T>(p0, p1);
           }
-          const float p0 = exp2f(s0), p1 = exp2f(s1);
-          l += p0 + p1;
-          packed[i >> 1] = pack_pair<T>(p0, p1);
+          ptx::tmem_st16(s_addr + c * 16, packed);
         }
-        ptx::tmem_st16(s_addr + c * 16, packed);
       }
       ptx::tmem_st_wait();
       ptx::tc_fence_before();
@@ -403,6 +466,7 @@ bool make_tensor_map_bhsd(CUtensorMap* map, const void* base, int64_t B, int64_t
     set_error("cuTensorMapEncodeTiled is not available from the driver");
     return false;
   }
+  bind_primary_context();
   // a dimension of extent 1 may carry any stride in torch; give it a well-formed one
   int64_t ss = st[2], sh = st[1], sb = st[0];
   if (S == 1) ss = D;

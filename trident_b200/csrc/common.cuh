@@ -41,6 +41,13 @@ static inline int launch_status(const char* what) {
   return 0;
 }
 
+// Driver-API entry points (tensor-map encoding) need the primary context bound to the calling
+// thread; a thread that has not yet made a runtime call (an autograd worker) may not have it.
+static inline void bind_primary_context() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) == cudaSuccess) cudaSetDevice(dev);
+}
+
 static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 static inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
 static inline size_t dtype_size(int dtype) { return dtype == TB200_F32 ? 4 : 2; }

@@ -325,6 +325,7 @@ bool make_tensor_map_2d(CUtensorMap* map, const void* base, uint64_t rows, uint6
     set_error("cuTensorMapEncodeTiled is not available from the driver");
     return false;
   }
+  bind_primary_context();
   cuuint64_t dims[2] = {cols, rows};
   cuuint64_t strides[1] = {ld * 2};
   cuuint32_t box[2] = {box_cols, box_rows};
@@ -347,6 +348,7 @@ bool make_tensor_map_3d(CUtensorMap* map, const void* base, uint64_t batch, uint
     set_error("cuTensorMapEncodeTiled is not available from the driver");
     return false;
   }
+  bind_primary_context();
   cuuint64_t dims[3] = {cols, rows, batch};
   cuuint64_t strides[2] = {ld * 2, batch_stride * 2};
   cuuint32_t box[3] = {box_cols, box_rows, 1};
