@@ -15,8 +15,11 @@
 //   dK  += dS^T Q_i             (A from TMEM, B = Q_i  read MN-major)    -> TMEM [kv][d]
 //   dQ_i = dS K_j               (A = dS^T in smem read MN-major, B = K_j MN-major)
 //                               -> TMEM [q][d], in the columns dP^T occupied
-//   drain warps (one thread per query row) add dQ_i into an fp32 accumulator in global
-//   memory with vector reductions; a last small kernel scales and rounds it.
+//   drain warps (one thread per query row) move dQ_i from tensor memory into the shared
+//   memory that Q_i and dO_i occupied (free once dK has consumed Q_i), and one thread adds it
+//   to an fp32 accumulator in global memory with bulk tensor reduce-add copies (the
+//   per-thread vector reductions this replaces were bound by uncoalesced 16-byte atomics);
+//   a last small kernel scales and rounds the accumulator.
 //
 // The MMA thread issues, per query tile s:  dP^T(s) | dV(s) | S^T(s+1) | dK(s) dQ(s), so the
 // tensor pipe always has the neighbouring tile's products to run while the compute warps are
@@ -41,7 +44,7 @@ bool make_tensor_map_bhsd(CUtensorMap* map, const void* base, int64_t B, int64_t
 
 namespace {
 
-constexpr int BWD_THREADS = 384;
+constexpr int BWD_THREADS = 512;
 constexpr float LOG2E = 1.4426950408889634f;
 
 struct BwdParams {
@@ -72,10 +75,24 @@ __device__ inline void bulk_load(void* smem_dst, const void* gsrc, uint32_t byte
                "l"(gsrc), "r"(bytes), "r"(ptx::smem_u32(bar))
                : "memory");
 }
-__device__ inline void red_add_v4(float* addr, float a, float b, float c, float d) {
-  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d)
+// Adds a [128 rows][32 floats] shared-memory box (128-byte swizzled) into a 2-D fp32 tensor.
+__device__ inline void tma_reduce_add_2d(const CUtensorMap* map, const void* smem_src, int x, int y) {
+#ifdef TB200_EXPERIMENT_PLAIN_STORE
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%1, %2}], [%3];" ::"l"(map),
+               "r"(x), "r"(y), "r"(ptx::smem_u32(smem_src))
+               : "memory");
+  return;
+#endif
+  asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%1, %2}], [%3];" ::"l"(map),
+               "r"(x), "r"(y), "r"(ptx::smem_u32(smem_src))
                : "memory");
 }
+__device__ inline void red_add_f32(float* addr, float v) {
+  asm volatile("red.global.add.f32 [%0], %1;" ::"l"(addr), "f"(v) : "memory");
+}
+__device__ inline void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ inline void bulk_wait_group_read0() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ inline void bulk_wait_group0() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 template <typename T>
 __device__ inline void unpack_pair(uint32_t v, float& lo, float& hi);
 template <>
@@ -94,7 +111,7 @@ template <typename T, int D, bool CAUSAL, bool MASKED>
 __global__ void __launch_bounds__(BWD_THREADS, 1)
     attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                        const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do,
-                       const BwdParams p) {
+                       const __grid_constant__ CUtensorMap map_dq, const BwdParams p) {
   constexpr int TILE_BYTES = 128 * D * 2;
   constexpr int NBOX = D / 64;
   constexpr int BOX_BYTES = 128 * 64 * 2;
@@ -103,6 +120,13 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
   constexpr uint32_t IDESC_ST = ptx::make_idesc(IS_BF16, false, false, 128, 128);   // K-major x K-major
   constexpr uint32_t IDESC_DKV = ptx::make_idesc(IS_BF16, false, true, 128, D);     // TMEM A, MN-major B
   constexpr uint32_t IDESC_DQ = ptx::make_idesc(IS_BF16, true, true, 128, D);       // MN-major x MN-major
+  // At D = 128 dQ_i is produced transposed, dQ^T = K_j^T dS^T (the same two descriptors with
+  // their roles swapped), so that a drain thread owns one feature d and a warp-level scalar
+  // reduction covers 128 contiguous bytes of one dQ row. At D = 64 (M = 64 is not used) dQ_i
+  // keeps the query index on the lanes and goes out through shared memory and a bulk
+  // tensor reduce-add.
+  constexpr bool DQ_T = (D == 128);
+  constexpr uint32_t IDESC_DQT = ptx::make_idesc(IS_BF16, true, true, 128, 128);
   constexpr uint32_t TMEM_COLS = 512;
   constexpr uint32_t COL_ST = 0, COL_DPT = 128, COL_DV = 256, COL_DK = 256 + D;
   constexpr uint32_t COL_DQ = COL_DPT;  // dQ_i reuses the dP^T columns once dS^T has been consumed
@@ -122,9 +146,9 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
   uint64_t* qdo_full = bars + 1;     // [2]
   uint64_t* qdo_empty = bars + 3;    // [2]
   uint64_t* st_ready = bars + 5;     // S^T(s) computed
-  uint64_t* p1_ready = bars + 6;     // P^T(s) written            (128 arrivals)
+  uint64_t* p1_ready = bars + 6;     // P^T(s) written            (256 arrivals)
   uint64_t* dpt_ready = bars + 7;    // dP^T(s) computed
-  uint64_t* p2_ready = bars + 8;     // dS^T(s) written           (128 arrivals)
+  uint64_t* p2_ready = bars + 8;     // dS^T(s) written           (256 arrivals)
   uint64_t* dq_ready = bars + 9;     // dQ(s) computed
   uint64_t* dq_drained = bars + 10;  // dQ(s) read out            (128 arrivals)
   uint64_t* all_done = bars + 11;
@@ -139,7 +163,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
   const int steps = p.nq - i_begin;
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < 12; ++i) ptx::mbar_init(&bars[i], (i == 6 || i == 8 || i == 10) ? 128 : 1);
+    for (int i = 0; i < 12; ++i) ptx::mbar_init(&bars[i], (i == 6 || i == 8) ? 256 : (i == 10 ? 128 : 1));
     *abort_flag = 0;
     if ((ptx::smem_u32(smem) & 1023u) != 0) {  // swizzled tiles need a 1024-byte aligned base
       *abort_flag = 1;
@@ -150,6 +174,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
     ptx::prefetch_tensormap(&map_k);
     ptx::prefetch_tensormap(&map_v);
     ptx::prefetch_tensormap(&map_do);
+    ptx::prefetch_tensormap(&map_dq);
   }
   if (warp == 2) {
     ptx::tmem_alloc(tmem_slot, TMEM_COLS);
@@ -169,7 +194,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
       tma_load_4d(v_smem + c * BOX_BYTES, &map_v, kv_full, c * 64, jt * 128, h, b);
     }
     for (int s = 0; s < steps; ++s) {
-      const int it = i_begin + s;
+      const int it = i_begin + (s + jt) % steps;  // staggered start: CTAs of one head add into different dQ tiles
       const int st = s & 1;
       ptx::mbar_wait(&qdo_empty[st], ((s >> 1) & 1) ^ 1, abort_flag, p.status, 41);
       ptx::mbar_expect_tx(&qdo_full[st], 2 * TILE_BYTES + 2 * 512);
@@ -236,17 +261,27 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
       for (int ks = 0; ks < 8; ++ks)
         ptx::umma_ts(tmem_base + COL_DK, tmem_base + COL_DPT + ks * 8,
                      ptx::make_smem_desc(qa + ks * 2048, BOX_BYTES, 1024), IDESC_DKV, (s | ks) != 0);
-      ptx::umma_commit(&qdo_empty[st]);
+      if constexpr (DQ_T) {
+        ptx::umma_commit(&qdo_empty[st]);
 #pragma unroll
-      for (int ks = 0; ks < 8; ++ks)  // reduction over the 128 key rows of the tile
-        ptx::umma_ss(tmem_base + COL_DQ, ptx::make_smem_desc(sa + ks * 2048, BOX_BYTES, 1024),
-                     ptx::make_smem_desc(ka + ks * 2048, BOX_BYTES, 1024), IDESC_DQ, ks != 0);
+        for (int ks = 0; ks < 8; ++ks)  // dQ^T = K_j^T dS^T, reduction over the 128 key rows
+          ptx::umma_ss(tmem_base + COL_DQ, ptx::make_smem_desc(ka + ks * 2048, BOX_BYTES, 1024),
+                       ptx::make_smem_desc(sa + ks * 2048, BOX_BYTES, 1024), IDESC_DQT, ks != 0);
+      } else {
+        // (the Q/dO stage is released by the drain warps, which first reuse it as dQ staging)
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks)  // reduction over the 128 key rows of the tile
+          ptx::umma_ss(tmem_base + COL_DQ, ptx::make_smem_desc(sa + ks * 2048, BOX_BYTES, 1024),
+                       ptx::make_smem_desc(ka + ks * 2048, BOX_BYTES, 1024), IDESC_DQ, ks != 0);
+      }
       ptx::umma_commit(dq_ready);
     }
     ptx::umma_commit(all_done);
-  } else if (warp >= 4 && warp < 8) {
+  } else if (warp >= 4 && warp < 12) {
     // ---------------------------------------------------------------- P^T / dS^T (lane = key row)
+    // warps 4-7 take the query columns [0, 64) of their rows, warps 8-11 the columns [64, 128)
     const int quarter = warp & 3;
+    const int half = (warp - 4) >> 2;
     const int r = quarter * 32 + lane;
     const int kv_g = jt * 128 + r;
     const uint32_t lane_off = static_cast<uint32_t>(quarter * 32) << 16;
@@ -258,11 +293,11 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
       mask_col = reinterpret_cast<const T*>(p.mask) + (long long)b * p.a.ms[0] + (long long)h * p.a.ms[1] +
                  (long long)kv_g * p.a.ms[3];
     for (int s = 0; s < steps; ++s) {
-      const int it = i_begin + s;
+      const int it = i_begin + (s + jt) % steps;  // staggered start: CTAs of one head add into different dQ tiles
       const int st = s & 1;
       const float4* nlse4 = reinterpret_cast<const float4*>(nlse_smem + st * 128);
       const float4* ndel4 = reinterpret_cast<const float4*>(ndelta_smem + st * 128);
-      uint32_t pp[64];  // P^T row of this thread, packed pairs along the query index
+      uint32_t pp[32];  // this thread's half row of P^T, packed pairs along the query index
       ptx::mbar_wait(&qdo_full[st], (s >> 1) & 1, abort_flag, p.status, 48);  // -lse, -delta of the tile
       ptx::mbar_wait(st_ready, s & 1, abort_flag, p.status, 49);
       ptx::tc_fence_after();
@@ -270,7 +305,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
       // ---- stage A: P^T = exp2(S^T * scale*log2e - lse*log2e)
       {
         uint32_t ra[32], rb[32];
-        auto stage_a = [&](const uint32_t (&sv)[32], int c) {
+        auto stage_a = [&](const uint32_t (&sv)[32], int c, int lc) {
 #pragma unroll
           for (int g = 0; g < 8; ++g) {
             const float4 nl = nlse4[c * 8 + g];
@@ -292,28 +327,26 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
               if (col + 2 < r) p2 = 0.f;
               if (col + 3 < r) p3 = 0.f;
             }
-            pp[c * 16 + g * 2] = am::cvt_pair<T>(p0, p1);
-            pp[c * 16 + g * 2 + 1] = am::cvt_pair<T>(p2, p3);
+            pp[lc * 16 + g * 2] = am::cvt_pair<T>(p0, p1);
+            pp[lc * 16 + g * 2 + 1] = am::cvt_pair<T>(p2, p3);
           }
         };
-        ptx::tmem_ld32(st_addr, ra);
+        const int c0 = 2 * half;
+        ptx::tmem_ld32(st_addr + c0 * 32, ra);
         am::tmem_ld_wait_dep(ra);
-        ptx::tmem_ld32(st_addr + 32, rb);
-        stage_a(ra, 0);
+        ptx::tmem_ld32(st_addr + c0 * 32 + 32, rb);
+        stage_a(ra, c0, 0);
         am::tmem_ld_wait_dep(rb);
-        ptx::tmem_ld32(st_addr + 64, ra);
-        stage_a(rb, 1);
-        am::tmem_ld_wait_dep(ra);
-        ptx::tmem_ld32(st_addr + 96, rb);
-        stage_a(ra, 2);
-        am::tmem_ld_wait_dep(rb);
-        stage_a(rb, 3);
+        stage_a(rb, c0 + 1, 1);
+        // both owners of a key row (this warp and its partner four warps away) must have read
+        // their S^T columns before either overwrites them with packed P^T
+        asm volatile("bar.sync 1, 256;" ::: "memory");
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
+        for (int lc = 0; lc < 2; ++lc) {
           uint32_t chunk[16];
 #pragma unroll
-          for (int i = 0; i < 16; ++i) chunk[i] = pp[c * 16 + i];
-          ptx::tmem_st16(st_addr + c * 16, chunk);
+          for (int i = 0; i < 16; ++i) chunk[i] = pp[lc * 16 + i];
+          ptx::tmem_st16(st_addr + (c0 + lc) * 16, chunk);
         }
         ptx::tmem_st_wait();
         ptx::tc_fence_before();
@@ -324,14 +357,14 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
       ptx::tc_fence_after();
       {
         uint32_t ra[32], rb[32];
-        auto stage_b = [&](const uint32_t (&dv)[32], int c) {
+        auto stage_b = [&](const uint32_t (&dv)[32], int c, int lc) {
           uint32_t dd[16];
 #pragma unroll
           for (int g = 0; g < 8; ++g) {
             const float4 nd = ndel4[c * 8 + g];
             float pa, pb, pc, pd;
-            unpack_pair<T>(pp[c * 16 + g * 2], pa, pb);
-            unpack_pair<T>(pp[c * 16 + g * 2 + 1], pc, pd);
+            unpack_pair<T>(pp[lc * 16 + g * 2], pa, pb);
+            unpack_pair<T>(pp[lc * 16 + g * 2 + 1], pc, pd);
             float d0, d1, d2, d3;
             am::unpack2f(am::mul2(am::pack2f(pa, pb),
                                   am::add2(am::pack2u(dv[g * 4], dv[g * 4 + 1]), am::pack2f(nd.x, nd.y))),
@@ -342,7 +375,8 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
             dd[g * 2] = am::cvt_pair<T>(d0, d1);
             dd[g * 2 + 1] = am::cvt_pair<T>(d2, d3);
           }
-          ptx::tmem_st16(dp_addr + c * 16, dd);
+#pragma unroll
+          for (int i = 0; i < 16; ++i) pp[lc * 16 + i] = dd[i];  // P^T is no longer needed
           // dS^T tile in shared memory: [key row][query], 64-query blocks of 16 KB, 128-byte
           // rows whose 16-byte chunks are XOR-swizzled with the row index (the layout a
           // 128-byte-swizzled tensor copy of a [128][64] box would produce)
@@ -354,18 +388,21 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
                 make_uint4(dd[g * 4 + 0], dd[g * 4 + 1], dd[g * 4 + 2], dd[g * 4 + 3]);
           }
         };
-        ptx::tmem_ld32(dp_addr, ra);
+        const int c0 = 2 * half;
+        ptx::tmem_ld32(dp_addr + c0 * 32, ra);
         am::tmem_ld_wait_dep(ra);
-        ptx::tmem_ld32(dp_addr + 32, rb);
-        stage_b(ra, 0);
+        ptx::tmem_ld32(dp_addr + c0 * 32 + 32, rb);
+        stage_b(ra, c0, 0);
         am::tmem_ld_wait_dep(rb);
-        ptx::tmem_ld32(dp_addr + 64, ra);
-        stage_b(rb, 1);
-        am::tmem_ld_wait_dep(ra);
-        ptx::tmem_ld32(dp_addr + 96, rb);
-        stage_b(ra, 2);
-        am::tmem_ld_wait_dep(rb);
-        stage_b(rb, 3);
+        stage_b(rb, c0 + 1, 1);
+        asm volatile("bar.sync 1, 256;" ::: "memory");  // dP^T fully read before dS^T overwrites it
+#pragma unroll
+        for (int lc = 0; lc < 2; ++lc) {
+          uint32_t chunk[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i) chunk[i] = pp[lc * 16 + i];
+          ptx::tmem_st16(dp_addr + (c0 + lc) * 16, chunk);
+        }
         ptx::tmem_st_wait();
         ptx::fence_proxy_async_smem();
         ptx::tc_fence_before();
@@ -379,9 +416,8 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
     T* dv_row = reinterpret_cast<T*>(p.dv) + out_row;
     T* dk_row = reinterpret_cast<T*>(p.dk) + out_row;
 #pragma unroll 1
-    for (int c = 0; c < 2 * D / 32; ++c) {
-      const bool is_k = c >= D / 32;
-      const int cc = is_k ? c - D / 32 : c;
+    for (int cc = 0; cc < D / 32; ++cc) {
+      const bool is_k = half == 1;  // warps 4-7 write dV, warps 8-11 write dK
       const float mul = is_k ? p.a.scale : 1.f;
       uint32_t rr[32];
       ptx::tmem_ld32(tmem_base + lane_off + (is_k ? COL_DK : COL_DV) + cc * 32, rr);
@@ -397,29 +433,75 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
         *reinterpret_cast<uint4*>(dst + g * 8) = o;
       }
     }
-  } else if (warp >= 8) {
+  } else if (warp >= 12) {
     // ---------------------------------------------------------------- dQ drain (lane = query row)
     const int quarter = warp & 3;
     const int r = quarter * 32 + lane;
     const uint32_t dq_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + COL_DQ;
+    const long long row_base = ((long long)b * p.a.H + h) * p.a.S;
     for (int s = 0; s < steps; ++s) {
-      const int it = i_begin + s;
+      const int it = i_begin + (s + jt) % steps;  // staggered start: CTAs of one head add into different dQ tiles
+      const int st = s & 1;
       ptx::mbar_wait(dq_ready, s & 1, abort_flag, p.status, 52);
       ptx::tc_fence_after();
-      float* dst = p.dq_acc + ((((long long)b * p.a.H + h) * p.a.S) + (long long)it * 128 + r) * D;
-#pragma unroll 1
-      for (int c = 0; c < D / 32; ++c) {
-        uint32_t rr[32];
-        ptx::tmem_ld32(dq_addr + c * 32, rr);
-        ptx::tmem_ld_wait();
+      if constexpr (DQ_T) {
+        // this thread owns feature d = r of the tile's 128 query rows
+        float* dst = p.dq_acc + (row_base + (long long)it * 128) * D + r;
 #pragma unroll
-        for (int g = 0; g < 8; ++g)
-          red_add_v4(dst + c * 32 + g * 4, __uint_as_float(rr[g * 4 + 0]), __uint_as_float(rr[g * 4 + 1]),
-                     __uint_as_float(rr[g * 4 + 2]), __uint_as_float(rr[g * 4 + 3]));
+        for (int c = 0; c < 4; c += 2) {
+          uint32_t r0[32], r1[32];
+          ptx::tmem_ld32(dq_addr + c * 32, r0);
+          ptx::tmem_ld32(dq_addr + c * 32 + 32, r1);
+          am::tmem_ld_wait_dep(r0);
+          am::tmem_ld_wait_dep(r1);
+          if (c == 2) {  // tensor memory released as soon as its values sit in registers
+            ptx::tc_fence_before();
+            ptx::mbar_arrive(dq_drained);
+          }
+#pragma unroll
+          for (int i = 0; i < 32; ++i) red_add_f32(dst + (long long)(c * 32 + i) * D, __uint_as_float(r0[i]));
+#pragma unroll
+          for (int i = 0; i < 32; ++i) red_add_f32(dst + (long long)(c * 32 + 32 + i) * D, __uint_as_float(r1[i]));
+        }
+        continue;
       }
-      ptx::tc_fence_before();
-      ptx::mbar_arrive(dq_drained);
+      // dQ(s) complete implies dK(s) complete (in-order pipe): Q_s and dO_s are dead, and their
+      // shared memory (D/32 boxes of [128 rows][32 floats], 16 KB each) stages dQ_i
+      uint8_t* stage_q = q_smem + st * TILE_BYTES;
+      uint8_t* stage_do = do_smem + st * TILE_BYTES;
+      auto box_ptr = [&](int j) { return (j < D / 64 ? stage_q : stage_do) + (j % (D / 64)) * 16384; };
+#pragma unroll
+      for (int c = 0; c < D / 32; c += 2) {
+        uint32_t r0[32], r1[32];
+        ptx::tmem_ld32(dq_addr + c * 32, r0);
+        ptx::tmem_ld32(dq_addr + c * 32 + 32, r1);
+        am::tmem_ld_wait_dep(r0);
+        am::tmem_ld_wait_dep(r1);
+        if (c + 2 >= D / 32) {  // tensor memory released as soon as its values sit in registers
+          ptx::tc_fence_before();
+          ptx::mbar_arrive(dq_drained);
+        }
+        uint8_t* row0 = box_ptr(c) + r * 128;
+        uint8_t* row1 = box_ptr(c + 1) + r * 128;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const int chunk = (k ^ (r & 7)) * 16;  // 128-byte swizzle: conflict-free and what the copy expects
+          *reinterpret_cast<uint4*>(row0 + chunk) = make_uint4(r0[k * 4], r0[k * 4 + 1], r0[k * 4 + 2], r0[k * 4 + 3]);
+          *reinterpret_cast<uint4*>(row1 + chunk) = make_uint4(r1[k * 4], r1[k * 4 + 1], r1[k * 4 + 2], r1[k * 4 + 3]);
+        }
+      }
+      ptx::fence_proxy_async_smem();
+      asm volatile("bar.sync 2, 128;" ::: "memory");
+      if (threadIdx.x == 12 * 32) {
+        const int y = (int)(row_base + (long long)it * 128);
+#pragma unroll
+        for (int j = 0; j < D / 32; ++j) tma_reduce_add_2d(&map_dq, box_ptr(j), j * 32, y);
+        bulk_commit_group();
+        bulk_wait_group_read0();          // staging read out: the producer may refill the stage
+        ptx::mbar_arrive(&qdo_empty[st]);
+      }
     }
+    if (threadIdx.x == 12 * 32) bulk_wait_group0();  // every reduce-add has landed before the CTA ends
   }
   ptx::tc_fence_before();
   __syncthreads();
@@ -467,9 +549,45 @@ __global__ void dq_convert_kernel(T* __restrict__ dq, const float* __restrict__ 
   *reinterpret_cast<uint4*>(dq + i) = pack<T>(v);
 }
 
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                              const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                              CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// 2-D map over the fp32 dq accumulator [rows, D], box [128 rows][32 floats], 128-byte swizzle.
+static bool make_dq_map(CUtensorMap* map, float* base, uint64_t rows, uint64_t D) {
+  static EncodeFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeFn>(sym);
+    else
+      cudaGetLastError();
+  });
+  if (!fn) {
+    set_error("cuTensorMapEncodeTiled is not available from the driver");
+    return false;
+  }
+  bind_primary_context();
+  cuuint64_t dims[2] = {D, rows};
+  cuuint64_t strides[1] = {D * 4};
+  cuuint32_t box[2] = {32, 128};
+  cuuint32_t elem[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, base, dims, strides, box, elem,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_error("cuTensorMapEncodeTiled (dq accumulator) failed with CUresult %d", (int)r);
+    return false;
+  }
+  return true;
+}
+
 template <typename T, int D, bool CAUSAL, bool MASKED>
 static int launch_bwd(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& md,
-                      const BwdParams& p, cudaStream_t st) {
+                      const CUtensorMap& mdq, const BwdParams& p, cudaStream_t st) {
   constexpr int SMEM = 6 * 128 * D * 2 + 128 * 128 * 2 + 2048 + 128;
   auto kern = attn_bwd_tc_kernel<T, D, CAUSAL, MASKED>;
   static std::once_flag once;
@@ -480,7 +598,7 @@ static int launch_bwd(const CUtensorMap& mq, const CUtensorMap& mk, const CUtens
     return (int)attr_err;
   }
   dim3 grid((unsigned)p.nq, (unsigned)(p.a.B * p.a.H));
-  kern<<<grid, BWD_THREADS, SMEM, st>>>(mq, mk, mv, md, p);
+  kern<<<grid, BWD_THREADS, SMEM, st>>>(mq, mk, mv, md, mdq, p);
   return launch_status("attn_bwd_tc");
 }
 
@@ -491,12 +609,13 @@ static int launch_bwd(const CUtensorMap& mq, const CUtensorMap& mk, const CUtens
 int launch_attn_bwd_tc(void* dq, void* dk, void* dv, const void* dout, const void* q, const void* k,
                        const void* v, const void* out, const float* lse, float* row_scratch, float* dq_acc,
                        const void* mask, const AttnArgs& a, int dtype, cudaStream_t st) {
-  CUtensorMap mq, mk, mv, md;
+  CUtensorMap mq, mk, mv, md, mdq;
   const int64_t ds[4] = {a.H * a.S * a.D, a.S * a.D, a.D, 1};  // dout is contiguous
   if (!make_tensor_map_bhsd(&mq, q, a.B, a.H, a.S, a.D, a.qs, 128) ||
       !make_tensor_map_bhsd(&mk, k, a.B, a.H, a.S, a.D, a.ks, 128) ||
       !make_tensor_map_bhsd(&mv, v, a.B, a.H, a.S, a.D, a.vs, 128) ||
-      !make_tensor_map_bhsd(&md, dout, a.B, a.H, a.S, a.D, ds, 128))
+      !make_tensor_map_bhsd(&md, dout, a.B, a.H, a.S, a.D, ds, 128) ||
+      !make_dq_map(&mdq, dq_acc, (uint64_t)(a.B * a.H * a.S), (uint64_t)a.D))
     return TB200_ERR_UNSUPPORTED;
   const long long rows = (long long)a.B * a.H * a.S;
   const long long n = rows * a.D;
@@ -526,11 +645,11 @@ int launch_attn_bwd_tc(void* dq, void* dk, void* dv, const void* dout, const voi
     int rc = launch_status("attn_bwd_prep");
     if (rc) return rc;
     if (a.causal)
-      rc = launch_bwd<T, D, true, false>(mq, mk, mv, md, p, st);
+      rc = launch_bwd<T, D, true, false>(mq, mk, mv, md, mdq, p, st);
     else if (mask)
-      rc = launch_bwd<T, D, false, true>(mq, mk, mv, md, p, st);
+      rc = launch_bwd<T, D, false, true>(mq, mk, mv, md, mdq, p, st);
     else
-      rc = launch_bwd<T, D, false, false>(mq, mk, mv, md, p, st);
+      rc = launch_bwd<T, D, false, false>(mq, mk, mv, md, mdq, p, st);
     if (rc) return rc;
     dq_convert_kernel<T><<<(unsigned)ceil_div(n, 8 * 256), 256, 0, st>>>((T*)dq, dq_acc, n, a.scale);
     return launch_status("dq_convert");
