@@ -58,16 +58,17 @@ def test_matches_regular_entry_point_on_two_calls_in_a_row(rows, cols, dtype, de
     want_first = _regular(*first)
     want_second = _regular(*second)
     torch.cuda.synchronize()
-    # dx takes the same arithmetic path in both entry points; the column sums are folded from
-    # a different number of partial rows, so they agree to fp32 summation-order accuracy
-    # (rtol = atol = 1e-5 scaled by sqrt(rows), as in tests/test_layer_norm.py)
+    # The two entry points may pick differently shaped kernels (the built-in scratch holds
+    # fewer partial rows than a caller's workspace), so row sums and column sums are folded
+    # in a different order: they agree to fp32 summation-order accuracy, plus one rounding of
+    # the output type (rtol = atol = 1e-5, the column sums scaled by sqrt(rows) as in
+    # tests/test_layer_norm.py).
     tol = 1e-5 * max(1.0, rows ** 0.5)
     for got, want in ((got_first, want_first), (got_second, want_second)):
-        assert torch.equal(got[0], want[0])
-        for g, w_, name in zip(got[1:], want[1:], ("dweight", "dbias")):
+        for g, w_, name in zip(got, want, ("dx", "dweight", "dbias")):
             g32, w32 = g.float(), w_.float()
             ulp = {torch.float32: 0.0, torch.float16: 2.0 ** -10, torch.bfloat16: 2.0 ** -7}[dtype]
-            bound = tol + (1e-5 + ulp) * w32.abs()
+            bound = (1e-5 if name == "dx" else tol) + (1e-5 + ulp) * w32.abs()
             assert ((g32 - w32).abs() <= bound).all(), f"{name}: {(g32 - w32).abs().max().item():.3e}"
 
 
@@ -76,7 +77,7 @@ def test_without_weight_and_bias_gradients(device):
     rows, cols = x.shape
     dx = torch.empty_like(x)
     _lib.layer_norm_bwd_static(dx, None, None, dy, x, w, mean, rstd, rows, cols)
-    assert torch.equal(dx, _regular(x, dy, w, mean, rstd)[0])
+    assert torch.allclose(dx, _regular(x, dy, w, mean, rstd)[0], rtol=1e-5, atol=1e-5)
 
 
 def test_rejects_rows_wider_than_the_built_in_scratch(device):

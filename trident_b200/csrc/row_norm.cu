@@ -23,6 +23,17 @@
 
 namespace tb200 {
 
+// Grouped backward kernels (defined at the end of this file): they take rows of up to 1024
+// vectors; *handled tells the caller whether they launched.
+int try_layer_norm_bwd_grouped(void* dx, void* dweight, void* dbias, const void* dy, const void* x,
+                               const void* weight, const float* mean, const float* rstd, void* workspace,
+                               size_t workspace_bytes, int64_t rows, int64_t cols, int dtype, cudaStream_t st,
+                               bool* handled);
+int try_rms_norm_bwd_grouped(void* dx, void* dweight, void* dbias, const void* dy, const void* x,
+                             const void* weight, const float* rms, void* workspace, size_t workspace_bytes,
+                             int64_t rows, int64_t cols, int64_t row_stride, int64_t col_stride,
+                             int64_t partial_cols, float eps, int dtype, cudaStream_t st, bool* handled);
+
 // ------------------------------------------------------------------ LayerNorm fwd
 template <typename T, int CHUNKS, bool CTA_ROW>
 __global__ void __launch_bounds__(CTA_ROW ? 512 : 256)
@@ -212,8 +223,9 @@ __global__ void norm_bwd_cols_generic(T* dw, T* db, const T* dy, const T* x, con
 }
 
 // ------------------------------------------------------------------ RMSNorm fwd
+// (two 512-thread CTAs per SM: the register cap roughly doubles the rows in flight)
 template <typename T, int CHUNKS, bool CTA_ROW>
-__global__ void __launch_bounds__(CTA_ROW ? 512 : 256)
+__global__ void __launch_bounds__(CTA_ROW ? 512 : 256, CTA_ROW ? 2 : 4)
     rms_fwd_vec(T* __restrict__ y, float* __restrict__ rms, const T* __restrict__ x,
                 const T* __restrict__ w, const T* __restrict__ b, int64_t rows, int cols,
                 int64_t row_stride, int partial, float eps) {
@@ -418,6 +430,12 @@ extern "C" int tb200_layer_norm_bwd(void* dx, void* dweight, void* dbias, const 
   TB200_REQUIRE(rows >= 0 && cols > 0, TB200_ERR_INVALID, "layer_norm_bwd: bad shape");
   cudaStream_t st = (cudaStream_t)stream;
   const bool want_cols = dweight || dbias;
+  {
+    bool handled = false;
+    int rc = try_layer_norm_bwd_grouped(dx, dweight, dbias, dy, x, weight, mean, rstd, workspace, workspace_bytes,
+                                        rows, cols, dtype, st, &handled);
+    if (rc || handled) return rc;
+  }
   return dispatch_dtype(dtype, [&](auto tag) -> int {
     using T = decltype(tag);
     const bool ok = aligned16(dx) && aligned16(dy) && aligned16(x) &&
@@ -520,6 +538,12 @@ extern "C" int tb200_rms_norm_bwd(void* dx, void* dweight, void* dbias, const vo
   TB200_REQUIRE(partial_cols > 0 && partial_cols <= cols, TB200_ERR_INVALID,
                 "rms_norm_bwd: partial_cols outside (0, cols]");
   cudaStream_t st = (cudaStream_t)stream;
+  {
+    bool handled = false;
+    int rc = try_rms_norm_bwd_grouped(dx, dweight, dbias, dy, x, weight, rms, workspace, workspace_bytes, rows,
+                                      cols, row_stride, col_stride, partial_cols, eps, dtype, st, &handled);
+    if (rc || handled) return rc;
+  }
   return dispatch_dtype(dtype, [&](auto tag) -> int {
     using T = decltype(tag);
     constexpr int VEC = Traits<T>::VEC;
@@ -629,6 +653,14 @@ extern "C" int tb200_layer_norm_bwd_static(void* dx, void* dweight, void* dbias,
   if (want_cols) {
     if (int rc = ln_static_scratch(&scratch)) return rc;
   }
+  {
+    // same kernel choice as tb200_layer_norm_bwd, with the built-in array as the workspace
+    bool handled = false;
+    int rc = try_layer_norm_bwd_grouped(dx, dweight, dbias, dy, x, weight, mean, rstd, scratch,
+                                        LN_STATIC_SCRATCH_FLOATS * sizeof(float), rows, cols, dtype, st,
+                                        &handled);
+    if (rc || handled) return rc;
+  }
   return dispatch_dtype(dtype, [&](auto tag) -> int {
     using T = decltype(tag);
     const bool ok = aligned16(dx) && aligned16(dy) && aligned16(x) && (!weight || aligned16(weight));
@@ -673,3 +705,324 @@ extern "C" int tb200_layer_norm_bwd_static(void* dx, void* dweight, void* dbias,
     return 0;
   });
 }
+
+// ---------------------------------------------------------------------------
+// Grouped backward kernel for LayerNorm and RMSNorm (rows of up to 1024 vectors).
+//
+// A 512-thread CTA is split into 512/TPR groups of TPR threads; every group owns one row at
+// a time, so a CTA keeps 512/TPR rows (x and dy) in flight and two CTAs fit on an SM. The grid
+// is bounded by twice the SM count, which bounds the fp32 [2, cols] partial rows of the
+// weight/bias gradients (one per CTA, folded over the CTA's groups in shared memory in a fixed
+// order). Each thread holds at most two 16-byte vectors per tensor, which keeps the register
+// footprint small enough for that occupancy.
+// ---------------------------------------------------------------------------
+namespace tb200 {
+
+template <int TPR>
+__device__ inline void group_barrier(int group) {
+  if constexpr (TPR > 32) asm volatile("bar.sync %0, %1;" ::"r"(group + 1), "n"(TPR) : "memory");
+}
+
+// Sums two values over the TPR threads of a group. `slots` holds [2 phases][16 warps][2].
+template <int TPR>
+__device__ inline void group_sum2(float& a, float& b, float* slots, int& phase, int group) {
+  a = warp_sum(a);
+  b = warp_sum(b);
+  if constexpr (TPR > 32) {
+    constexpr int WPG = TPR / 32;  // warps per group
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    float* s = slots + phase * 32;
+    phase ^= 1;
+    if (lane == 0) {
+      s[warp * 2] = a;
+      s[warp * 2 + 1] = b;
+    }
+    group_barrier<TPR>(group);
+    const int w0 = group * WPG;
+    float ra = 0.f, rb = 0.f;
+#pragma unroll
+    for (int w = 0; w < WPG; ++w) {
+      ra += s[(w0 + w) * 2];
+      rb += s[(w0 + w) * 2 + 1];
+    }
+    a = ra;
+    b = rb;
+  }
+}
+
+template <typename T, int CHUNKS, int TPR, bool RMS, bool WANT_B>
+__global__ void __launch_bounds__(512, 2)
+    norm_bwd_grouped(T* __restrict__ dx, float* __restrict__ partial, const T* __restrict__ dy,
+                     const T* __restrict__ x, const T* __restrict__ w, const float* __restrict__ stat_a,
+                     const float* __restrict__ stat_b, int64_t rows, int cols, int64_t x_row_stride,
+                     int partial_cols, float eps, int want_cols) {
+  constexpr int VEC = Traits<T>::VEC;
+  constexpr int GROUPS = 512 / TPR;
+  extern __shared__ __align__(16) float colbuf[];  // [2][cols], used after the row loop
+  __shared__ float slots[64];
+  int phase = 0;
+  const int group = threadIdx.x / TPR, tid = threadIdx.x % TPR;
+  const float inv_n = 1.f / (float)cols;
+  // With 16 elements per thread the weights do not fit the 64-register budget next to the
+  // two accumulators: they are then re-read per row (an L1 hit) instead of being kept.
+  constexpr bool KEEP_W = CHUNKS * VEC <= 8;
+  float acc_w[CHUNKS][VEC], acc_b[WANT_B ? CHUNKS : 1][VEC], ws[CHUNKS][VEC];
+  auto load_w = [&](float (&dst)[CHUNKS][VEC]) {
+#pragma unroll
+    for (int c = 0; c < CHUNKS; ++c) {
+      const int col = (c * TPR + tid) * VEC;
+      if (w && col < cols) unpack<T>(ld_cached(w + col), dst[c]);
+#pragma unroll
+      for (int i = 0; i < VEC; ++i)
+        if (!w || col >= cols) dst[c][i] = 1.f;  // out-of-range columns carry dy = 0
+    }
+  };
+  if constexpr (KEEP_W) load_w(ws);
+#pragma unroll
+  for (int c = 0; c < CHUNKS; ++c)
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) {
+      acc_w[c][i] = 0.f;
+      if constexpr (WANT_B) acc_b[c][i] = 0.f;
+    }
+  // every group runs the same number of iterations (the group barrier needs all its threads,
+  // and out-of-range rows are simply predicated off)
+  const int64_t row_step = (int64_t)gridDim.x * GROUPS;
+  for (int64_t row0 = (int64_t)blockIdx.x * GROUPS; row0 < rows; row0 += row_step) {
+    const int64_t row = row0 + group;
+    const bool live = row < rows;
+    float xs[CHUNKS][VEC], gs[CHUNKS][VEC];
+    uint4 rx[CHUNKS], rg[CHUNKS];
+#pragma unroll
+    for (int c = 0; c < CHUNKS; ++c) {
+      const int col = (c * TPR + tid) * VEC;
+      if (live && col < cols) {
+        rx[c] = ld_stream(x + row * x_row_stride + col);
+        rg[c] = ld_stream(dy + row * cols + col);
+      } else {
+        rx[c] = make_uint4(0, 0, 0, 0);
+        rg[c] = make_uint4(0, 0, 0, 0);
+      }
+    }
+    const float sa = live ? stat_a[row] : 0.f;
+    const float sb = (!RMS && live) ? stat_b[row] : 0.f;
+#pragma unroll
+    for (int c = 0; c < CHUNKS; ++c) {
+      unpack<T>(rx[c], xs[c]);
+      unpack<T>(rg[c], gs[c]);
+    }
+    if constexpr (!KEEP_W) load_w(ws);
+    if constexpr (!RMS) {
+      // LayerNorm: sa = mean, sb = rstd
+      float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+      for (int c = 0; c < CHUNKS; ++c) {
+        const bool in = live && (c * TPR + tid) * VEC < cols;
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) {
+          const float xh = in ? (xs[c][i] - sa) * sb : 0.f;
+          const float d = gs[c][i];
+          acc_w[c][i] += d * xh;
+          if constexpr (WANT_B) acc_b[c][i] += d;
+          const float g = d * ws[c][i];
+          xs[c][i] = xh;
+          gs[c][i] = g;
+          s1 += g * xh;
+          s2 += g;
+        }
+      }
+      group_sum2<TPR>(s1, s2, slots, phase, group);
+      const float c1 = s1 * inv_n, c2 = s2 * inv_n;
+#pragma unroll
+      for (int c = 0; c < CHUNKS; ++c)
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) xs[c][i] = sb * (gs[c][i] - xs[c][i] * c1 - c2);
+    } else {
+      // RMSNorm: sa = rms
+      const float inv = live ? 1.f / (sa + eps) : 0.f;
+      float s = 0.f, unused = 0.f;
+#pragma unroll
+      for (int c = 0; c < CHUNKS; ++c)
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) {
+          const float d = gs[c][i];
+          acc_w[c][i] += d * xs[c][i] * inv;
+          if constexpr (WANT_B) acc_b[c][i] += d;
+          const float g = d * ws[c][i];
+          gs[c][i] = g;
+          s += g * xs[c][i];
+        }
+      group_sum2<TPR>(s, unused, slots, phase, group);
+      const float k = sa > 0.f ? s * inv * inv / ((float)partial_cols * sa) : 0.f;
+#pragma unroll
+      for (int c = 0; c < CHUNKS; ++c) {
+        const int col = (c * TPR + tid) * VEC;
+#pragma unroll
+        for (int i = 0; i < VEC; ++i)
+          xs[c][i] = gs[c][i] * inv - ((col + i < partial_cols) ? xs[c][i] * k : 0.f);
+      }
+    }
+    if (live) {
+#pragma unroll
+      for (int c = 0; c < CHUNKS; ++c) {
+        const int col = (c * TPR + tid) * VEC;
+        if (col < cols) st_stream(dx + row * cols + col, pack<T>(xs[c]));
+      }
+    }
+  }
+  if (want_cols) {
+    // fold the groups of this CTA in a fixed order, then write its [2, cols] partial row
+    for (int g = 0; g < GROUPS; ++g) {
+      if (group == g) {
+#pragma unroll
+        for (int c = 0; c < CHUNKS; ++c) {
+          const int col = (c * TPR + tid) * VEC;
+          if (col < cols) {
+#pragma unroll
+            for (int i = 0; i < VEC; ++i) {
+              const float bv = WANT_B ? acc_b[WANT_B ? c : 0][i] : 0.f;
+              if (g == 0) {
+                colbuf[col + i] = acc_w[c][i];
+                colbuf[cols + col + i] = bv;
+              } else {
+                colbuf[col + i] += acc_w[c][i];
+                colbuf[cols + col + i] += bv;
+              }
+            }
+          }
+        }
+      }
+      __syncthreads();
+    }
+    float* out = partial + (int64_t)blockIdx.x * 2 * cols;
+    for (int i = threadIdx.x * 4; i < 2 * cols; i += 512 * 4)
+      *reinterpret_cast<float4*>(out + i) = *reinterpret_cast<const float4*>(colbuf + i);
+  }
+}
+
+struct GroupedPlan {
+  bool ok = false;
+  int tpr = 32, chunks = 1;
+};
+
+template <typename T>
+static GroupedPlan plan_grouped(int64_t cols, bool ptrs_ok) {
+  GroupedPlan p;
+  constexpr int VEC = Traits<T>::VEC;
+  if (!ptrs_ok || cols <= 0 || cols % VEC != 0) return p;
+  const int64_t vecs = cols / VEC;
+  for (int tpr : {32, 128, 256, 512}) {
+    if ((int64_t)tpr * 2 >= vecs) {
+      p.ok = true;
+      p.tpr = tpr;
+      p.chunks = vecs > tpr ? 2 : 1;
+      return p;
+    }
+  }
+  return p;
+}
+
+// Launches the grouped kernel; returns the number of partial rows written (the grid size) in
+// *nparts. `grid_cap` bounds the grid (the workspace of the caller must hold that many rows).
+template <typename T, bool RMS, bool WANT_B>
+static int launch_grouped(const GroupedPlan& gp, T* dx, float* partial, const T* dy, const T* x, const T* w,
+                          const float* stat_a, const float* stat_b, int64_t rows, int64_t cols,
+                          int64_t x_row_stride, int64_t partial_cols, float eps, bool want_cols,
+                          int64_t grid_cap, int* nparts, cudaStream_t st) {
+  const int groups = 512 / gp.tpr;
+  int64_t grid = ceil_div(rows, groups);
+  if (grid > grid_cap) grid = grid_cap;
+  if (grid < 1) grid = 1;
+  *nparts = (int)grid;
+  const size_t smem = want_cols ? (size_t)2 * cols * sizeof(float) : 0;
+  auto go = [&](auto kern) -> int {
+    if (smem > 48 * 1024) {
+      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (e != cudaSuccess) {
+        set_error("norm_bwd_grouped: cudaFuncSetAttribute failed: %s", cudaGetErrorString(e));
+        return (int)e;
+      }
+    }
+    kern<<<(unsigned)grid, 512, smem, st>>>(dx, partial, dy, x, w, stat_a, stat_b, rows, (int)cols, x_row_stride,
+                                            (int)partial_cols, eps, want_cols ? 1 : 0);
+    return launch_status("norm_bwd_grouped");
+  };
+  switch (gp.tpr * 10 + gp.chunks) {
+    case 321: return go(norm_bwd_grouped<T, 1, 32, RMS, WANT_B>);
+    case 322: return go(norm_bwd_grouped<T, 2, 32, RMS, WANT_B>);
+    case 1281: return go(norm_bwd_grouped<T, 1, 128, RMS, WANT_B>);
+    case 1282: return go(norm_bwd_grouped<T, 2, 128, RMS, WANT_B>);
+    case 2561: return go(norm_bwd_grouped<T, 1, 256, RMS, WANT_B>);
+    case 2562: return go(norm_bwd_grouped<T, 2, 256, RMS, WANT_B>);
+    case 5121: return go(norm_bwd_grouped<T, 1, 512, RMS, WANT_B>);
+    case 5122: return go(norm_bwd_grouped<T, 2, 512, RMS, WANT_B>);
+  }
+  set_error("internal: bad grouped plan");
+  return TB200_ERR_INVALID;
+}
+
+int try_layer_norm_bwd_grouped(void* dx, void* dweight, void* dbias, const void* dy, const void* x,
+                               const void* weight, const float* mean, const float* rstd, void* workspace,
+                               size_t workspace_bytes, int64_t rows, int64_t cols, int dtype, cudaStream_t st,
+                               bool* handled) {
+  *handled = false;
+  const bool want_cols = dweight || dbias;
+  return dispatch_dtype(dtype, [&](auto tag) -> int {
+    using T = decltype(tag);
+    const bool ok = aligned16(dx) && aligned16(dy) && aligned16(x) && (!weight || aligned16(weight)) &&
+                    (!want_cols || (workspace && aligned16(workspace))) && rows > 0;
+    GroupedPlan gp = plan_grouped<T>(cols, ok);
+    if (!gp.ok) return 0;
+    int64_t cap = (int64_t)sm_count() * 2;
+    if (want_cols) {
+      const int64_t fit = (int64_t)(workspace_bytes / ((size_t)2 * cols * sizeof(float)));
+      if (fit < 1) return 0;
+      if (cap > fit) cap = fit;
+    }
+    int nparts = 0;
+    int rc = launch_grouped<T, false, true>(gp, (T*)dx, (float*)workspace, (const T*)dy, (const T*)x, (const T*)weight,
+                                      mean, rstd, rows, cols, cols, cols, 0.f, want_cols, cap, &nparts, st);
+    if (rc) return rc;
+    if (want_cols) {
+      rc = finalize_cols<T>((T*)dweight, (T*)dbias, (const float*)workspace, nparts, cols, st);
+      if (rc) return rc;
+    }
+    note_kernel("row_vec", want_cols ? 2 : 1);
+    *handled = true;
+    return 0;
+  });
+}
+
+int try_rms_norm_bwd_grouped(void* dx, void* dweight, void* dbias, const void* dy, const void* x,
+                             const void* weight, const float* rms, void* workspace, size_t workspace_bytes,
+                             int64_t rows, int64_t cols, int64_t row_stride, int64_t col_stride,
+                             int64_t partial_cols, float eps, int dtype, cudaStream_t st, bool* handled) {
+  *handled = false;
+  return dispatch_dtype(dtype, [&](auto tag) -> int {
+    using T = decltype(tag);
+    constexpr int VEC = Traits<T>::VEC;
+    const bool ok = aligned16(dx) && aligned16(dy) && aligned16(x) && aligned16(weight) && col_stride == 1 &&
+                    row_stride % VEC == 0 && row_stride >= cols && workspace && aligned16(workspace) && rows > 0;
+    GroupedPlan gp = plan_grouped<T>(cols, ok);
+    if (!gp.ok) return 0;
+    int64_t cap = (int64_t)sm_count() * 2;
+    const int64_t fit = (int64_t)(workspace_bytes / ((size_t)2 * cols * sizeof(float)));
+    if (fit < 1) return 0;
+    if (cap > fit) cap = fit;
+    int nparts = 0;
+    int rc = dbias ? launch_grouped<T, true, true>(gp, (T*)dx, (float*)workspace, (const T*)dy, (const T*)x,
+                                                   (const T*)weight, rms, nullptr, rows, cols, row_stride,
+                                                   partial_cols, eps, true, cap, &nparts, st)
+                   : launch_grouped<T, true, false>(gp, (T*)dx, (float*)workspace, (const T*)dy, (const T*)x,
+                                                    (const T*)weight, rms, nullptr, rows, cols, row_stride,
+                                                    partial_cols, eps, true, cap, &nparts, st);
+    if (rc) return rc;
+    rc = finalize_cols<T>((T*)dweight, (T*)dbias, (const float*)workspace, nparts, cols, st);
+    if (rc) return rc;
+    note_kernel("row_vec", 2);
+    *handled = true;
+    return 0;
+  });
+}
+
+}  // namespace tb200
