@@ -911,8 +911,11 @@ static GroupedPlan plan_grouped(int64_t cols, bool ptrs_ok) {
   constexpr int VEC = Traits<T>::VEC;
   if (!ptrs_ok || cols <= 0 || cols % VEC != 0) return p;
   const int64_t vecs = cols / VEC;
+  // 16-bit rows keep one vector (8 elements) per thread when they fit 512 threads: two vectors
+  // per thread do not fit the 64-register budget of two resident CTAs without spilling
+  const int per_thread = (sizeof(T) == 2 && vecs <= 512) ? 1 : 2;
   for (int tpr : {32, 128, 256, 512}) {
-    if ((int64_t)tpr * 2 >= vecs) {
+    if ((int64_t)tpr * per_thread >= vecs) {
       p.ok = true;
       p.tpr = tpr;
       p.chunks = vecs > tpr ? 2 : 1;
