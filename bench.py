@@ -52,6 +52,27 @@ CPU_SAMPLE = {
 }
 
 
+_JSON_FD = None
+
+
+def capture_stdout():
+    """Routes everything libraries print on stdout (NCCL's version banner, for one) to stderr, so
+    that the only thing on stdout is the one JSON line written by emit()."""
+    global _JSON_FD
+    if _JSON_FD is None:
+        sys.stdout.flush()
+        _JSON_FD = os.dup(1)
+        os.dup2(2, 1)
+
+
+def emit(line):
+    sys.stdout.flush()
+    if _JSON_FD is None:
+        print(json.dumps(line), flush=True)
+    else:
+        os.write(_JSON_FD, (json.dumps(line) + "\n").encode())
+
+
 def peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -389,7 +410,7 @@ def run_reference(args, wl):
                          "sample": text + "; torch eager CPU (the oracle the reference's tests use)"},
         "e2e": {"value": value, "unit": unit_of(wl), "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
-    print(json.dumps(line), flush=True)
+    emit(line)
 
 
 def measure(wl, args, rank, world, device, with_cpu, sampler=None):
@@ -460,6 +481,8 @@ def main():
     args = ap.parse_args()
 
     rank, local, world = dist_env()
+    if not (args.gpus > 1 and world == 1):
+        capture_stdout()
     if args.gpus > 1 and world == 1:
         os.execvp(sys.executable, [sys.executable, "-m", "torch.distributed.run", "--nnodes=1",
                                    f"--nproc-per-node={args.gpus}", "--master-addr", "127.0.0.1",
@@ -504,7 +527,7 @@ def main():
     if extra:
         line["workloads"] = extra
     if rank == 0:
-        print(json.dumps(line), flush=True)
+        emit(line)
     if world > 1:
         import torch.distributed as dist
 
