@@ -46,7 +46,12 @@ static inline RowPlan plan_rows(int64_t cols, bool ptrs_ok, int cta_max_chunks =
   constexpr int MAXC = max_chunks<T>();
   if (!ptrs_ok || cols % VEC != 0 || cols <= 0) return p;
   const int64_t vecs = cols / VEC;
-  if (vecs <= 32 * MAXC) {
+  // A warp owns a row only while two vectors per lane cover it: wider rows in one warp need so
+  // many registers that a single 8-warp CTA fits on an SM and too few rows are in flight
+  // (measured: 1024 fp32 columns per warp reached 2.9 TB/s, the same row split over a
+  // 128-thread CTA behaves like the softmax kernels, which run at the HBM roofline).
+  (void)MAXC;
+  if (vecs <= 64) {
     p.vec = true;
     p.cta_row = false;
     p.chunks = next_pow2(ceil_div(vecs, 32));

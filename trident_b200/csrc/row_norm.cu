@@ -35,8 +35,11 @@ int try_rms_norm_bwd_grouped(void* dx, void* dweight, void* dbias, const void* d
                              int64_t partial_cols, float eps, int dtype, cudaStream_t st, bool* handled);
 
 // ------------------------------------------------------------------ LayerNorm fwd
+// The row stays packed in registers (16-byte vectors as loaded) and is unpacked once per
+// pass (sum, centred squares, output): for 16-bit rows that halves the live registers, which
+// is what decides how many rows an SM keeps in flight.
 template <typename T, int CHUNKS, bool CTA_ROW>
-__global__ void __launch_bounds__(CTA_ROW ? 512 : 256)
+__global__ void __launch_bounds__(CTA_ROW ? 512 : 256, CTA_ROW ? 2 : 4)
     ln_fwd_vec(T* __restrict__ y, float* __restrict__ mean, float* __restrict__ rstd,
                const T* __restrict__ x, const T* __restrict__ w, const T* __restrict__ b,
                int64_t rows, int cols, float eps) {
@@ -46,43 +49,55 @@ __global__ void __launch_bounds__(CTA_ROW ? 512 : 256)
   RowThread<CTA_ROW> rt;
   const float inv_n = 1.f / (float)cols;
   for (int64_t row = rt.first_row(); row < rows; row += rt.row_step()) {
-    float xs[CHUNKS][VEC];
-    load_row<T, CHUNKS, CTA_ROW>(xs, x + row * cols, cols, rt);
+    uint4 raw[CHUNKS];
+    const T* xr = x + row * cols;
+#pragma unroll
+    for (int c = 0; c < CHUNKS; ++c) {
+      const int col = rt.template col<VEC>(c);
+      raw[c] = col < cols ? ld_stream(xr + col) : make_uint4(0, 0, 0, 0);
+    }
     float s = 0.f;
 #pragma unroll
-    for (int c = 0; c < CHUNKS; ++c)
+    for (int c = 0; c < CHUNKS; ++c) {
+      float t[VEC];
+      unpack<T>(raw[c], t);
 #pragma unroll
-      for (int i = 0; i < VEC; ++i) s += xs[c][i];
+      for (int i = 0; i < VEC; ++i) s += t[i];
+    }
     const float mu = row_reduce<CTA_ROW, false>(s, slot, phase) * inv_n;
     float v = 0.f;
 #pragma unroll
     for (int c = 0; c < CHUNKS; ++c) {
       const bool in = rt.template col<VEC>(c) < cols;
+      float t[VEC];
+      unpack<T>(raw[c], t);
 #pragma unroll
       for (int i = 0; i < VEC; ++i) {
-        const float d = xs[c][i] - mu;
+        const float d = t[i] - mu;
         v += in ? d * d : 0.f;
       }
     }
     const float var = row_reduce<CTA_ROW, false>(v, slot, phase) * inv_n;
     const float rs = rsqrtf(var + eps);
+    T* yr = y + row * cols;
 #pragma unroll
     for (int c = 0; c < CHUNKS; ++c) {
       const int col = rt.template col<VEC>(c);
       if (col < cols) {
-        float ws[VEC], bs[VEC];
+        float t[VEC], ws[VEC], bs[VEC];
+        unpack<T>(raw[c], t);
         if (w) unpack<T>(ld_cached(w + col), ws);
         if (b) unpack<T>(ld_cached(b + col), bs);
 #pragma unroll
         for (int i = 0; i < VEC; ++i) {
-          float o = (xs[c][i] - mu) * rs;
+          float o = (t[i] - mu) * rs;
           if (w) o *= ws[i];
           if (b) o += bs[i];
-          xs[c][i] = o;
+          t[i] = o;
         }
+        st_stream(yr + col, pack<T>(t));
       }
     }
-    store_row<T, CHUNKS, CTA_ROW>(y + row * cols, xs, cols, rt);
     if (rt.tid == 0) {
       mean[row] = mu;
       rstd[row] = rs;
@@ -763,21 +778,10 @@ __global__ void __launch_bounds__(512, 2)
   int phase = 0;
   const int group = threadIdx.x / TPR, tid = threadIdx.x % TPR;
   const float inv_n = 1.f / (float)cols;
-  // With 16 elements per thread the weights do not fit the 64-register budget next to the
-  // two accumulators: they are then re-read per row (an L1 hit) instead of being kept.
-  constexpr bool KEEP_W = CHUNKS * VEC <= 8;
-  float acc_w[CHUNKS][VEC], acc_b[WANT_B ? CHUNKS : 1][VEC], ws[CHUNKS][VEC];
-  auto load_w = [&](float (&dst)[CHUNKS][VEC]) {
-#pragma unroll
-    for (int c = 0; c < CHUNKS; ++c) {
-      const int col = (c * TPR + tid) * VEC;
-      if (w && col < cols) unpack<T>(ld_cached(w + col), dst[c]);
-#pragma unroll
-      for (int i = 0; i < VEC; ++i)
-        if (!w || col >= cols) dst[c][i] = 1.f;  // out-of-range columns carry dy = 0
-    }
-  };
-  if constexpr (KEEP_W) load_w(ws);
+  // The row (x and dy) stays packed in registers as loaded and is unpacked once per pass; the
+  // weights are re-read per pass (L1 hits). Live state per thread: two packed rows and the
+  // fp32 column accumulators.
+  float acc_w[CHUNKS][VEC], acc_b[WANT_B ? CHUNKS : 1][VEC];
 #pragma unroll
   for (int c = 0; c < CHUNKS; ++c)
 #pragma unroll
@@ -785,13 +789,20 @@ __global__ void __launch_bounds__(512, 2)
       acc_w[c][i] = 0.f;
       if constexpr (WANT_B) acc_b[c][i] = 0.f;
     }
+  auto load_w = [&](float (&dst)[VEC], int col) {
+    if (w && col < cols) {
+      unpack<T>(ld_cached(w + col), dst);
+    } else {
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) dst[i] = 1.f;  // out-of-range columns carry dy = 0
+    }
+  };
   // every group runs the same number of iterations (the group barrier needs all its threads,
   // and out-of-range rows are simply predicated off)
   const int64_t row_step = (int64_t)gridDim.x * GROUPS;
   for (int64_t row0 = (int64_t)blockIdx.x * GROUPS; row0 < rows; row0 += row_step) {
     const int64_t row = row0 + group;
     const bool live = row < rows;
-    float xs[CHUNKS][VEC], gs[CHUNKS][VEC];
     uint4 rx[CHUNKS], rg[CHUNKS];
 #pragma unroll
     for (int c = 0; c < CHUNKS; ++c) {
@@ -806,27 +817,24 @@ __global__ void __launch_bounds__(512, 2)
     }
     const float sa = live ? stat_a[row] : 0.f;
     const float sb = (!RMS && live) ? stat_b[row] : 0.f;
-#pragma unroll
-    for (int c = 0; c < CHUNKS; ++c) {
-      unpack<T>(rx[c], xs[c]);
-      unpack<T>(rg[c], gs[c]);
-    }
-    if constexpr (!KEEP_W) load_w(ws);
     if constexpr (!RMS) {
       // LayerNorm: sa = mean, sb = rstd
       float s1 = 0.f, s2 = 0.f;
 #pragma unroll
       for (int c = 0; c < CHUNKS; ++c) {
-        const bool in = live && (c * TPR + tid) * VEC < cols;
+        const int col = (c * TPR + tid) * VEC;
+        const bool in = live && col < cols;
+        float xs[VEC], gs[VEC], wv[VEC];
+        unpack<T>(rx[c], xs);
+        unpack<T>(rg[c], gs);
+        load_w(wv, col);
 #pragma unroll
         for (int i = 0; i < VEC; ++i) {
-          const float xh = in ? (xs[c][i] - sa) * sb : 0.f;
-          const float d = gs[c][i];
+          const float xh = in ? (xs[i] - sa) * sb : 0.f;
+          const float d = gs[i];
           acc_w[c][i] += d * xh;
           if constexpr (WANT_B) acc_b[c][i] += d;
-          const float g = d * ws[c][i];
-          xs[c][i] = xh;
-          gs[c][i] = g;
+          const float g = d * wv[i];
           s1 += g * xh;
           s2 += g;
         }
@@ -834,39 +842,48 @@ __global__ void __launch_bounds__(512, 2)
       group_sum2<TPR>(s1, s2, slots, phase, group);
       const float c1 = s1 * inv_n, c2 = s2 * inv_n;
 #pragma unroll
-      for (int c = 0; c < CHUNKS; ++c)
+      for (int c = 0; c < CHUNKS; ++c) {
+        const int col = (c * TPR + tid) * VEC;
+        float xs[VEC], gs[VEC], wv[VEC];
+        unpack<T>(rx[c], xs);
+        unpack<T>(rg[c], gs);
+        load_w(wv, col);
 #pragma unroll
-        for (int i = 0; i < VEC; ++i) xs[c][i] = sb * (gs[c][i] - xs[c][i] * c1 - c2);
+        for (int i = 0; i < VEC; ++i) xs[i] = sb * (gs[i] * wv[i] - (xs[i] - sa) * sb * c1 - c2);
+        if (live && col < cols) st_stream(dx + row * cols + col, pack<T>(xs));
+      }
     } else {
       // RMSNorm: sa = rms
       const float inv = live ? 1.f / (sa + eps) : 0.f;
       float s = 0.f, unused = 0.f;
 #pragma unroll
-      for (int c = 0; c < CHUNKS; ++c)
+      for (int c = 0; c < CHUNKS; ++c) {
+        const int col = (c * TPR + tid) * VEC;
+        float xs[VEC], gs[VEC], wv[VEC];
+        unpack<T>(rx[c], xs);
+        unpack<T>(rg[c], gs);
+        load_w(wv, col);
 #pragma unroll
         for (int i = 0; i < VEC; ++i) {
-          const float d = gs[c][i];
-          acc_w[c][i] += d * xs[c][i] * inv;
+          const float d = gs[i];
+          acc_w[c][i] += d * xs[i] * inv;
           if constexpr (WANT_B) acc_b[c][i] += d;
-          const float g = d * ws[c][i];
-          gs[c][i] = g;
-          s += g * xs[c][i];
+          s += d * wv[i] * xs[i];
         }
+      }
       group_sum2<TPR>(s, unused, slots, phase, group);
       const float k = sa > 0.f ? s * inv * inv / ((float)partial_cols * sa) : 0.f;
 #pragma unroll
       for (int c = 0; c < CHUNKS; ++c) {
         const int col = (c * TPR + tid) * VEC;
+        float xs[VEC], gs[VEC], wv[VEC];
+        unpack<T>(rx[c], xs);
+        unpack<T>(rg[c], gs);
+        load_w(wv, col);
 #pragma unroll
         for (int i = 0; i < VEC; ++i)
-          xs[c][i] = gs[c][i] * inv - ((col + i < partial_cols) ? xs[c][i] * k : 0.f);
-      }
-    }
-    if (live) {
-#pragma unroll
-      for (int c = 0; c < CHUNKS; ++c) {
-        const int col = (c * TPR + tid) * VEC;
-        if (col < cols) st_stream(dx + row * cols + col, pack<T>(xs[c]));
+          xs[i] = gs[i] * wv[i] * inv - ((col + i < partial_cols) ? xs[i] * k : 0.f);
+        if (live && col < cols) st_stream(dx + row * cols + col, pack<T>(xs));
       }
     }
   }
@@ -905,15 +922,19 @@ struct GroupedPlan {
   int tpr = 32, chunks = 1;
 };
 
+// `two_per_thread_16bit`: 16-bit rows may put two vectors on a thread. That fits the
+// 64-register budget only when a single column accumulator is kept (RMSNorm without bias
+// gradient: measured 57 us against 61 us on bf16 [8192, 4096]); with both accumulators it
+// spills and is slower (LayerNorm: 89 us against 59 us), so those cases keep one vector.
 template <typename T>
-static GroupedPlan plan_grouped(int64_t cols, bool ptrs_ok) {
+static GroupedPlan plan_grouped(int64_t cols, bool ptrs_ok, bool two_per_thread_16bit) {
   GroupedPlan p;
   constexpr int VEC = Traits<T>::VEC;
   if (!ptrs_ok || cols <= 0 || cols % VEC != 0) return p;
   const int64_t vecs = cols / VEC;
   // 16-bit rows keep one vector (8 elements) per thread when they fit 512 threads: two vectors
   // per thread do not fit the 64-register budget of two resident CTAs without spilling
-  const int per_thread = (sizeof(T) == 2 && vecs <= 512) ? 1 : 2;
+  const int per_thread = (sizeof(T) == 2 && vecs <= 512 && !two_per_thread_16bit) ? 1 : 2;
   for (int tpr : {32, 128, 256, 512}) {
     if ((int64_t)tpr * per_thread >= vecs) {
       p.ok = true;
@@ -974,7 +995,7 @@ int try_layer_norm_bwd_grouped(void* dx, void* dweight, void* dbias, const void*
     using T = decltype(tag);
     const bool ok = aligned16(dx) && aligned16(dy) && aligned16(x) && (!weight || aligned16(weight)) &&
                     (!want_cols || (workspace && aligned16(workspace))) && rows > 0;
-    GroupedPlan gp = plan_grouped<T>(cols, ok);
+    GroupedPlan gp = plan_grouped<T>(cols, ok, false);
     if (!gp.ok) return 0;
     int64_t cap = (int64_t)sm_count() * 2;
     if (want_cols) {
@@ -1006,7 +1027,7 @@ int try_rms_norm_bwd_grouped(void* dx, void* dweight, void* dbias, const void* d
     constexpr int VEC = Traits<T>::VEC;
     const bool ok = aligned16(dx) && aligned16(dy) && aligned16(x) && aligned16(weight) && col_stride == 1 &&
                     row_stride % VEC == 0 && row_stride >= cols && workspace && aligned16(workspace) && rows > 0;
-    GroupedPlan gp = plan_grouped<T>(cols, ok);
+    GroupedPlan gp = plan_grouped<T>(cols, ok, dbias == nullptr);
     if (!gp.ok) return 0;
     int64_t cap = (int64_t)sm_count() * 2;
     const int64_t fit = (int64_t)(workspace_bytes / ((size_t)2 * cols * sizeof(float)));
