@@ -55,6 +55,8 @@ struct BwdParams {
   const float* nlse2;   // [B,H,S]  -lse * log2(e)
   const float* ndelta;  // [B,H,S]  -sum_d out*dout
   const void* mask;
+  int mask_tma;         // the mask tile is staged in shared memory by bulk tensor copies
+  int mask_has_b, mask_has_h;  // 0 when that mask dimension is broadcast
   int* status;
   float scale_log2;
   int nq;
@@ -111,7 +113,8 @@ template <typename T, int D, bool CAUSAL, bool MASKED>
 __global__ void __launch_bounds__(BWD_THREADS, 1)
     attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                        const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do,
-                       const __grid_constant__ CUtensorMap map_dq, const BwdParams p) {
+                       const __grid_constant__ CUtensorMap map_dq, const __grid_constant__ CUtensorMap map_mask,
+                       const BwdParams p) {
   constexpr int TILE_BYTES = 128 * D * 2;
   constexpr int NBOX = D / 64;
   constexpr int BOX_BYTES = 128 * 64 * 2;
@@ -127,6 +130,11 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
   // tensor reduce-add.
   constexpr bool DQ_T = (D == 128);
   constexpr uint32_t IDESC_DQT = ptx::make_idesc(IS_BF16, true, true, 128, 128);
+  // At D = 64 there is shared memory left for a double-buffered [128 q][128 kv] mask tile,
+  // fetched with the Q/dO tile; the compute threads then read their key column from shared
+  // memory instead of issuing one global load per query row.
+  constexpr bool MASK_SMEM = MASKED && D == 64;
+  constexpr int MASK_TILE_BYTES = 128 * 128 * 2;
   constexpr uint32_t TMEM_COLS = 512;
   constexpr uint32_t COL_ST = 0, COL_DPT = 128, COL_DV = 256, COL_DK = 256 + D;
   constexpr uint32_t COL_DQ = COL_DPT;  // dQ_i reuses the dP^T columns once dS^T has been consumed
@@ -139,7 +147,9 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
   uint8_t* q_smem = smem + 2 * TILE_BYTES;    // [2]
   uint8_t* do_smem = smem + 4 * TILE_BYTES;   // [2]
   uint8_t* ds_smem = smem + 6 * TILE_BYTES;
-  float* nlse_smem = reinterpret_cast<float*>(smem + 6 * TILE_BYTES + DS_BYTES);  // [2][128]
+  uint8_t* mask_smem = smem + 6 * TILE_BYTES + DS_BYTES;  // [2][MASK_TILE_BYTES] when MASK_SMEM
+  float* nlse_smem =
+      reinterpret_cast<float*>(smem + 6 * TILE_BYTES + DS_BYTES + (MASK_SMEM ? 2 * MASK_TILE_BYTES : 0));  // [2][128]
   float* ndelta_smem = nlse_smem + 256;                                           // [2][128]
   uint64_t* bars = reinterpret_cast<uint64_t*>(ndelta_smem + 256);
   uint64_t* kv_full = bars + 0;
@@ -197,7 +207,14 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
       const int it = i_begin + (s + jt) % steps;  // staggered start: CTAs of one head add into different dQ tiles
       const int st = s & 1;
       ptx::mbar_wait(&qdo_empty[st], ((s >> 1) & 1) ^ 1, abort_flag, p.status, 41);
-      ptx::mbar_expect_tx(&qdo_full[st], 2 * TILE_BYTES + 2 * 512);
+      const bool stage_mask = MASK_SMEM && p.mask_tma;
+      ptx::mbar_expect_tx(&qdo_full[st], 2 * TILE_BYTES + 2 * 512 + (stage_mask ? MASK_TILE_BYTES : 0));
+      if (stage_mask) {
+#pragma unroll
+        for (int bx = 0; bx < 2; ++bx)
+          tma_load_4d(mask_smem + st * MASK_TILE_BYTES + bx * BOX_BYTES, &map_mask, &qdo_full[st],
+                      jt * 128 + 64 * bx, it * 128, p.mask_has_h ? h : 0, p.mask_has_b ? b : 0);
+      }
 #pragma unroll
       for (int c = 0; c < NBOX; ++c) {
         tma_load_4d(q_smem + st * TILE_BYTES + c * BOX_BYTES, &map_q, &qdo_full[st], c * 64, it * 128, h, b);
@@ -313,11 +330,22 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
             am::unpack2f(am::fma2(am::pack2u(sv[g * 4], sv[g * 4 + 1]), scale2, am::pack2f(nl.x, nl.y)), x0, x1);
             am::unpack2f(am::fma2(am::pack2u(sv[g * 4 + 2], sv[g * 4 + 3]), scale2, am::pack2f(nl.z, nl.w)), x2, x3);
             if constexpr (MASKED) {
-              const long long q0 = (long long)it * 128 + c * 32 + g * 4;
-              x0 += Traits<T>::to_f(mask_col[(q0 + 0) * p.a.ms[2]]) * LOG2E;
-              x1 += Traits<T>::to_f(mask_col[(q0 + 1) * p.a.ms[2]]) * LOG2E;
-              x2 += Traits<T>::to_f(mask_col[(q0 + 2) * p.a.ms[2]]) * LOG2E;
-              x3 += Traits<T>::to_f(mask_col[(q0 + 3) * p.a.ms[2]]) * LOG2E;
+              if (MASK_SMEM && p.mask_tma) {
+                // element (q, kv = r) of the 128-byte swizzled [128 q][64 kv] boxes
+                const int qc = c * 32 + g * 4;
+                const uint8_t* mt = mask_smem + st * MASK_TILE_BYTES + (r >> 6) * BOX_BYTES + (r & 7) * 2;
+                const int kchunk = (r & 63) >> 3;
+                x0 += Traits<T>::to_f(*reinterpret_cast<const T*>(mt + (qc + 0) * 128 + ((kchunk ^ ((qc + 0) & 7)) << 4))) * LOG2E;
+                x1 += Traits<T>::to_f(*reinterpret_cast<const T*>(mt + (qc + 1) * 128 + ((kchunk ^ ((qc + 1) & 7)) << 4))) * LOG2E;
+                x2 += Traits<T>::to_f(*reinterpret_cast<const T*>(mt + (qc + 2) * 128 + ((kchunk ^ ((qc + 2) & 7)) << 4))) * LOG2E;
+                x3 += Traits<T>::to_f(*reinterpret_cast<const T*>(mt + (qc + 3) * 128 + ((kchunk ^ ((qc + 3) & 7)) << 4))) * LOG2E;
+              } else {
+                const long long q0 = (long long)it * 128 + c * 32 + g * 4;
+                x0 += Traits<T>::to_f(mask_col[(q0 + 0) * p.a.ms[2]]) * LOG2E;
+                x1 += Traits<T>::to_f(mask_col[(q0 + 1) * p.a.ms[2]]) * LOG2E;
+                x2 += Traits<T>::to_f(mask_col[(q0 + 2) * p.a.ms[2]]) * LOG2E;
+                x3 += Traits<T>::to_f(mask_col[(q0 + 3) * p.a.ms[2]]) * LOG2E;
+              }
             }
             float p0 = am::ex2(x0), p1 = am::ex2(x1), p2 = am::ex2(x2), p3 = am::ex2(x3);
             if (diag) {  // query index below the key index contributes nothing
@@ -587,8 +615,8 @@ static bool make_dq_map(CUtensorMap* map, float* base, uint64_t rows, uint64_t D
 
 template <typename T, int D, bool CAUSAL, bool MASKED>
 static int launch_bwd(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& md,
-                      const CUtensorMap& mdq, const BwdParams& p, cudaStream_t st) {
-  constexpr int SMEM = 6 * 128 * D * 2 + 128 * 128 * 2 + 2048 + 128;
+                      const CUtensorMap& mdq, const CUtensorMap& mmask, const BwdParams& p, cudaStream_t st) {
+  constexpr int SMEM = 6 * 128 * D * 2 + 128 * 128 * 2 + 2048 + 128 + ((MASKED && D == 64) ? 2 * 128 * 128 * 2 : 0);
   auto kern = attn_bwd_tc_kernel<T, D, CAUSAL, MASKED>;
   static std::once_flag once;
   static cudaError_t attr_err = cudaSuccess;
@@ -598,7 +626,7 @@ static int launch_bwd(const CUtensorMap& mq, const CUtensorMap& mk, const CUtens
     return (int)attr_err;
   }
   dim3 grid((unsigned)p.nq, (unsigned)(p.a.B * p.a.H));
-  kern<<<grid, BWD_THREADS, SMEM, st>>>(mq, mk, mv, md, mdq, p);
+  kern<<<grid, BWD_THREADS, SMEM, st>>>(mq, mk, mv, md, mdq, mmask, p);
   return launch_status("attn_bwd_tc");
 }
 
@@ -627,6 +655,18 @@ int launch_attn_bwd_tc(void* dq, void* dk, void* dv, const void* dout, const voi
     return (int)e;
   }
   BwdParams p;
+  CUtensorMap mmask = mq;  // placeholder when no mask tile is staged
+  p.mask_tma = 0;
+  p.mask_has_b = mask && a.ms[0] != 0;
+  p.mask_has_h = mask && a.ms[1] != 0;
+  if (mask && a.D == 64 && a.ms[3] == 1 && aligned16(mask) && a.ms[2] % 8 == 0 &&
+      (!p.mask_has_h || a.ms[1] % 8 == 0) && (!p.mask_has_b || a.ms[0] % 8 == 0)) {
+    // the mask seen as [Bm, Hm, S(query), S(key)] with its broadcast dimensions collapsed to 1
+    const int64_t mst[4] = {a.ms[0], a.ms[1], a.ms[2], 1};
+    if (!make_tensor_map_bhsd(&mmask, mask, p.mask_has_b ? a.B : 1, p.mask_has_h ? a.H : 1, a.S, a.S, mst, 128))
+      return TB200_ERR_UNSUPPORTED;
+    p.mask_tma = 1;
+  }
   p.a = a;
   p.dk = dk;
   p.dv = dv;
@@ -645,11 +685,11 @@ int launch_attn_bwd_tc(void* dq, void* dk, void* dv, const void* dout, const voi
     int rc = launch_status("attn_bwd_prep");
     if (rc) return rc;
     if (a.causal)
-      rc = launch_bwd<T, D, true, false>(mq, mk, mv, md, mdq, p, st);
+      rc = launch_bwd<T, D, true, false>(mq, mk, mv, md, mdq, mmask, p, st);
     else if (mask)
-      rc = launch_bwd<T, D, false, true>(mq, mk, mv, md, mdq, p, st);
+      rc = launch_bwd<T, D, false, true>(mq, mk, mv, md, mdq, mmask, p, st);
     else
-      rc = launch_bwd<T, D, false, false>(mq, mk, mv, md, mdq, p, st);
+      rc = launch_bwd<T, D, false, false>(mq, mk, mv, md, mdq, mmask, p, st);
     if (rc) return rc;
     dq_convert_kernel<T><<<(unsigned)ceil_div(n, 8 * 256), 256, 0, st>>>((T*)dq, dq_acc, n, a.scale);
     return launch_status("dq_convert");

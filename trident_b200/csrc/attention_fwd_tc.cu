@@ -272,9 +272,31 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
                  row_g * p.a.ms[2];
     float m_used = -INFINITY, l = 0.f;
     for (int j = 0; j < n; ++j) {
+      const long long kv0 = (long long)j * TK;
+      // the 128 mask values of this row and key tile are fetched before the scores are waited
+      // for, so their latency hides behind the QK^T product (16-byte loads, kept packed)
+      uint4 mraw[MASKED ? 16 : 1];
+      if constexpr (MASKED) {
+        if (p.mask_vec) {
+#pragma unroll
+          for (int c = 0; c < 16; ++c) mraw[c] = __ldg(reinterpret_cast<const uint4*>(mask_row + kv0 + c * 8));
+        }
+      }
+      auto mask32 = [&](float (&mv)[32], int c) {
+        if (p.mask_vec) {
+#pragma unroll
+          for (int jv = 0; jv < 4; ++jv) {
+            float f[8];
+            unpack<T>(mraw[MASKED ? c * 4 + jv : 0], f);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) mv[jv * 8 + i] = f[i] * LOG2E;
+          }
+        } else {
+          load_mask32<T>(mv, mask_row, kv0 + c * 32, p.a.ms[3], false);
+        }
+      };
       ptx::mbar_wait(&s_full[t], j & 1, abort_flag, p.status, 31);
       ptx::tc_fence_after();
-      const long long kv0 = (long long)j * TK;
       const bool diag = CAUSAL && (j == n - 1);
       // pass 1: row maximum of the scaled (and masked) scores, in log2 units
       float mx = -INFINITY;
@@ -306,13 +328,13 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
         mx = fmaxf(m0, m1) * p.scale_log2;
       } else {
         const int lim = CAUSAL ? row_in_tile : 1 << 30;  // columns above `lim` are masked (diagonal tile)
-#pragma unroll 1
+#pragma unroll
         for (int c = 0; c < 4; ++c) {
           uint32_t r[32];
           ptx::tmem_ld32(s_addr + c * 32, r);
           ptx::tmem_ld_wait();
           float mv[32];
-          if constexpr (MASKED) load_mask32<T>(mv, mask_row, kv0 + c * 32, p.a.ms[3], p.mask_vec != 0);
+          if constexpr (MASKED) mask32(mv, c);
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
             float s = __uint_as_float(r[i]) * p.scale_log2;
@@ -389,13 +411,13 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
         l += l0 + l1;
       } else {
         const int lim = CAUSAL ? row_in_tile : 1 << 30;
-#pragma unroll 1
+#pragma unroll
         for (int c = 0; c < 4; ++c) {
           uint32_t r[32];
           ptx::tmem_ld32(s_addr + c * 32, r);
           ptx::tmem_ld_wait();
           float mv[32];
-          if constexpr (MASKED) load_mask32<T>(mv, mask_row, kv0 + c * 32, p.a.ms[3], p.mask_vec != 0);
+          if constexpr (MASKED) mask32(mv, c);
           uint32_t packed[16];
 #pragma unroll
           for (int i = 0; i < 32; i += 2) {
