@@ -271,6 +271,22 @@ def time_e2e(wl, tensors, steps, warmup, world, device):
     return reduce_max(start.elapsed_time(stop), world, device) / 1e3, h2d, d2h
 
 
+# DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) of one full-size launch of each
+# workload's dominant kernel, from the ncu captures summarised under profiles/. A launch captured
+# on a quarter of the (batch, head) slices is scaled by 4: the slices are independent, so the traffic
+# grows in proportion. Bytes still in L2 when the kernel ends are not in these figures. None: not captured.
+NCU_TRAFFIC = {
+    "softmax": (368.2e6, "profiles/softmax_bwd_vec_fp16_16384x4096.md"),
+    "masked_softmax": (367.5e6, "profiles/masked_softmax_vec_fp16_16384x4096.md"),
+    "layer_norm": (36.1e6, "profiles/norm_kernels_layer_norm_fp32_4096x1024_rms_norm_bf16_8192x4096.md"),
+    "rms_norm": (176.2e6, "profiles/norm_kernels_layer_norm_fp32_4096x1024_rms_norm_bf16_8192x4096.md"),
+    "attention_causal": (4 * 289.9e6, "profiles/attn_tc_kernels_bf16_causal_S4096_D128.md (32 of 128 slices, x4)"),
+    "geglu": (None, "profiles/gemm_tc_kernel_bf16_geglu_2048x4096x22016.md (quarter of the rows: 301.0e6; "
+                    "the weight traffic does not scale with rows)"),
+    "attention_masked": (None, "not captured: the full-size mask alone is 8.6 GB"),
+}
+
+
 def dominant_kernel(wl, tensors):
     """(label, launch closure, algorithmic work per launch) of the workload's dominant kernel,
     called directly through the ctypes binding of the C ABI."""
@@ -292,7 +308,7 @@ def dominant_kernel(wl, tensors):
         dw, db = torch.empty_like(w), torch.empty_like(w)
         ws = torch.empty(_lib.layer_norm_bwd_workspace(rows, cols), dtype=torch.uint8, device=dev)
         _lib.layer_norm_fwd(y, mean, rstd, x, w, tensors["b"], rows, cols, 1e-5)
-        return ("ln_bwd_vec(+finalize)",
+        return ("norm_bwd_grouped + colsum_finalize",
                 lambda: _lib.layer_norm_bwd(dx, dw, db, dy, x, w, mean, rstd, ws, rows, cols),
                 3.0 * x.numel() * x.element_size())
     if wl.name == "rms_norm":
@@ -303,7 +319,7 @@ def dominant_kernel(wl, tensors):
         dw = torch.empty_like(w)
         ws = torch.empty(_lib.rms_norm_bwd_workspace(rows, cols), dtype=torch.uint8, device=dev)
         _lib.rms_norm_fwd(y, rms, x, w, None, rows, cols, cols, 1, cols, 1e-6)
-        return ("rms_bwd_vec(+finalize)",
+        return ("norm_bwd_grouped + colsum_finalize",
                 lambda: _lib.rms_norm_bwd(dx, dw, None, dy, x, w, rms, ws, rows, cols, cols, 1, cols, 1e-6),
                 3.0 * x.numel() * x.element_size())
     if wl.name == "geglu":
@@ -435,6 +451,9 @@ def measure(wl, args, rank, world, device, with_cpu, sampler=None):
     label, kwork, ksecs, l2note = time_dominant(wl, sets, min(args.steps, 20), args.warmup)
     del sets[1:]
     achieved = rate(wl, kwork, ksecs)
+    traffic, traffic_src = NCU_TRAFFIC.get(wl.name, (None, "not captured"))
+    if args.scale != 1 and traffic is not None:
+        traffic = traffic / args.scale
     e2e_steps = max(3, min(args.steps, 10))
     esecs, h2d, d2h = time_e2e(wl, tensors, e2e_steps, 1, world, device)
     e2e_value = rate(wl, work_total * e2e_steps, esecs)
@@ -450,7 +469,8 @@ def measure(wl, args, rank, world, device, with_cpu, sampler=None):
                    "shard": f"each of {world} rank(s) runs one full-size replica (replica = rank)"},
         "step_frac_of_peak": value / (peak * world),
         "roofline": {"bound": wl.bound, "kernel": label, "achieved": achieved, "peak": peak,
-                     "unit": unit_of(wl), "frac": achieved / peak, "traffic": None,
+                     "unit": unit_of(wl), "frac": achieved / peak, "traffic": traffic,
+                     "traffic_source": traffic_src,
                      "peak_source": pk["source"], "l2": l2note, "seconds_per_launch": ksecs},
         "e2e": {"value": e2e_value, "unit": unit_of(wl), "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "steps": e2e_steps},
