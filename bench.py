@@ -308,7 +308,7 @@ def dominant_kernel(wl, tensors):
         dw, db = torch.empty_like(w), torch.empty_like(w)
         ws = torch.empty(_lib.layer_norm_bwd_workspace(rows, cols), dtype=torch.uint8, device=dev)
         _lib.layer_norm_fwd(y, mean, rstd, x, w, tensors["b"], rows, cols, 1e-5)
-        return ("norm_bwd_grouped + colsum_finalize",
+        return ("norm_bwd_grouped (fused column sums)",
                 lambda: _lib.layer_norm_bwd(dx, dw, db, dy, x, w, mean, rstd, ws, rows, cols),
                 3.0 * x.numel() * x.element_size())
     if wl.name == "rms_norm":
@@ -319,7 +319,7 @@ def dominant_kernel(wl, tensors):
         dw = torch.empty_like(w)
         ws = torch.empty(_lib.rms_norm_bwd_workspace(rows, cols), dtype=torch.uint8, device=dev)
         _lib.rms_norm_fwd(y, rms, x, w, None, rows, cols, cols, 1, cols, 1e-6)
-        return ("norm_bwd_grouped + colsum_finalize",
+        return ("norm_bwd_grouped (fused column sums)",
                 lambda: _lib.rms_norm_bwd(dx, dw, None, dy, x, w, rms, ws, rows, cols, cols, 1, cols, 1e-6),
                 3.0 * x.numel() * x.element_size())
     if wl.name == "geglu":

@@ -205,6 +205,11 @@ int tb200_device_status(int reset);
 /* Force the CUDA-core kernels (1) or let the dispatcher choose (0). Used by tests to
  * cross-check the tensor-core kernels against the simple ones. Returns the old value. */
 int tb200_set_force_simt(int on);
+/* The norm backward kernels fold their per-CTA weight/bias gradient rows inside the same
+ * (cooperative) launch when on != 0 (the default), or in a second finalize kernel when
+ * on == 0. Both orders of summation are fixed. Used by tests to cover both paths (the
+ * second is otherwise only taken when the grid cannot be co-resident). Returns the old value. */
+int tb200_set_norm_fused_finalize(int on);
 
 #ifdef __cplusplus
 }

@@ -29,6 +29,7 @@ SIGNATURES = {
     "tb200_last_kernel": (ctypes.c_char_p, []),
     "tb200_last_launch_count": (c_int, []),
     "tb200_set_force_simt": (c_int, [c_int]),
+    "tb200_set_norm_fused_finalize": (c_int, [c_int]),
     "tb200_total_launches": (c_i64, []),
     "tb200_device_status": (c_int, [c_int]),
     "tb200_layer_norm_fwd": (c_int, [c_ptr] * 6 + [c_i64, c_i64, c_f32, c_int, c_ptr]),
@@ -107,6 +108,12 @@ def device_status(reset=False):
 
 def set_force_simt(on):
     return load().tb200_set_force_simt(1 if on else 0)
+
+
+def set_norm_fused_finalize(on):
+    """Norm backward: fold the weight/bias gradient inside the main launch (default) or in a
+    second kernel. Returns the old setting."""
+    return load().tb200_set_norm_fused_finalize(1 if on else 0)
 
 
 def dtype_code(dtype):

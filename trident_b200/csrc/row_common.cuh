@@ -15,6 +15,7 @@
 
 #include <type_traits>
 
+#include "attn_math.cuh"
 #include "common.cuh"
 
 namespace tb200 {
@@ -99,6 +100,60 @@ static inline int dispatch_plan(const RowPlan& p, Fn&& fn) {
   return TB200_ERR_INVALID;
 }
 
+// A 16-byte vector of T as fp32 pairs packed in 64-bit registers, for the two-lane fp32
+// instructions (fma/mul/add .f32x2): they halve the arithmetic instruction count of the row
+// kernels, which are close to issue-bound once their loads are in flight.
+template <typename T>
+__device__ inline void unpack2(const uint4& raw, uint64_t (&out)[Traits<T>::VEC / 2]);
+template <>
+__device__ inline void unpack2<float>(const uint4& raw, uint64_t (&out)[2]) {
+  out[0] = am::pack2u(raw.x, raw.y);
+  out[1] = am::pack2u(raw.z, raw.w);
+}
+template <>
+__device__ inline void unpack2<__nv_bfloat16>(const uint4& raw, uint64_t (&out)[4]) {
+  const uint32_t* w = reinterpret_cast<const uint32_t*>(&raw);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) out[i] = am::pack2u(w[i] << 16, w[i] & 0xffff0000u);
+}
+template <>
+__device__ inline void unpack2<__half>(const uint4& raw, uint64_t (&out)[4]) {
+  const __half2* h = reinterpret_cast<const __half2*>(&raw);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 f = __half22float2(h[i]);
+    out[i] = am::pack2f(f.x, f.y);
+  }
+}
+template <typename T>
+__device__ inline uint4 pack2(const uint64_t (&in)[Traits<T>::VEC / 2]) {
+  uint4 r;
+  uint32_t* w = reinterpret_cast<uint32_t*>(&r);
+  if constexpr (sizeof(T) == 4) {
+    float a, b;
+    am::unpack2f(in[0], a, b);
+    w[0] = __float_as_uint(a);
+    w[1] = __float_as_uint(b);
+    am::unpack2f(in[1], a, b);
+    w[2] = __float_as_uint(a);
+    w[3] = __float_as_uint(b);
+  } else {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      float a, b;
+      am::unpack2f(in[i], a, b);
+      w[i] = am::cvt_pair<T>(a, b);
+    }
+  }
+  return r;
+}
+__device__ inline uint64_t splat2(float v) { return am::pack2f(v, v); }
+__device__ inline float hsum2(uint64_t v) {
+  float a, b;
+  am::unpack2f(v, a, b);
+  return a + b;
+}
+
 // Position of the calling thread inside the row decomposition.
 template <bool CTA_ROW>
 struct RowThread {
@@ -180,8 +235,17 @@ __global__ void colsum_finalize_kernel(T* out_a, T* out_b, const float* partial,
   const int col = blockIdx.x * 32 + threadIdx.x;
   float acc = 0.f;
   if (col < cols) {
-    for (int p = threadIdx.y; p < nparts; p += 32)
-      acc += partial[((int64_t)p * gridDim.y + which) * cols + col];
+    // eight independent loads per trip: the kernel is a chain of load latencies otherwise
+    for (int p0 = threadIdx.y; p0 < nparts; p0 += 32 * 8) {
+      float v[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int p = p0 + 32 * j;
+        v[j] = p < nparts ? __ldg(partial + ((int64_t)p * gridDim.y + which) * cols + col) : 0.f;
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc += v[j];
+    }
   }
   tile[threadIdx.y][threadIdx.x] = acc;
   __syncthreads();

@@ -19,6 +19,10 @@
 // write y), backward 3*e (read x and dy, write dx); the weight-gradient column sums add
 // one fp32 partial row per CTA (grid bounded by the SM count), reduced by a second small
 // kernel.
+#include <cooperative_groups.h>
+
+#include <type_traits>
+
 #include "row_common.cuh"
 
 namespace tb200 {
@@ -28,7 +32,7 @@ namespace tb200 {
 int try_layer_norm_bwd_grouped(void* dx, void* dweight, void* dbias, const void* dy, const void* x,
                                const void* weight, const float* mean, const float* rstd, void* workspace,
                                size_t workspace_bytes, int64_t rows, int64_t cols, int dtype, cudaStream_t st,
-                               bool* handled);
+                               bool* handled, bool allow_fused);
 int try_rms_norm_bwd_grouped(void* dx, void* dweight, void* dbias, const void* dy, const void* x,
                              const void* weight, const float* rms, void* workspace, size_t workspace_bytes,
                              int64_t rows, int64_t cols, int64_t row_stride, int64_t col_stride,
@@ -56,46 +60,63 @@ __global__ void __launch_bounds__(CTA_ROW ? 512 : 256, CTA_ROW ? 2 : 4)
       const int col = rt.template col<VEC>(c);
       raw[c] = col < cols ? ld_stream(xr + col) : make_uint4(0, 0, 0, 0);
     }
-    float s = 0.f;
+    // weight and bias are requested before the reductions, so that their (L2) latency hides
+    // behind the row's own load instead of following the second barrier
+    // (only while the registers allow it)
+    constexpr bool EARLY = CHUNKS == 1 || (CHUNKS == 2 && sizeof(T) == 4);
+    uint4 wraw[EARLY ? CHUNKS : 1], braw[EARLY ? CHUNKS : 1];
+    if constexpr (EARLY) {
 #pragma unroll
-    for (int c = 0; c < CHUNKS; ++c) {
-      float t[VEC];
-      unpack<T>(raw[c], t);
-#pragma unroll
-      for (int i = 0; i < VEC; ++i) s += t[i];
-    }
-    const float mu = row_reduce<CTA_ROW, false>(s, slot, phase) * inv_n;
-    float v = 0.f;
-#pragma unroll
-    for (int c = 0; c < CHUNKS; ++c) {
-      const bool in = rt.template col<VEC>(c) < cols;
-      float t[VEC];
-      unpack<T>(raw[c], t);
-#pragma unroll
-      for (int i = 0; i < VEC; ++i) {
-        const float d = t[i] - mu;
-        v += in ? d * d : 0.f;
+      for (int c = 0; c < CHUNKS; ++c) {
+        const int col = rt.template col<VEC>(c);
+        wraw[c] = (w && col < cols) ? ld_cached(w + col) : make_uint4(0, 0, 0, 0);
+        braw[c] = (b && col < cols) ? ld_cached(b + col) : make_uint4(0, 0, 0, 0);
       }
     }
-    const float var = row_reduce<CTA_ROW, false>(v, slot, phase) * inv_n;
+    constexpr int PAIRS = VEC / 2;  // arithmetic on fp32 pairs (two-lane instructions)
+    uint64_t s2 = 0ull;
+#pragma unroll
+    for (int c = 0; c < CHUNKS; ++c) {
+      uint64_t t[PAIRS];
+      unpack2<T>(raw[c], t);
+#pragma unroll
+      for (int i = 0; i < PAIRS; ++i) s2 = am::add2(s2, t[i]);
+    }
+    const float mu = row_reduce<CTA_ROW, false>(hsum2(s2), slot, phase) * inv_n;
+    const uint64_t nmu2 = splat2(-mu);
+    uint64_t v2 = 0ull;
+#pragma unroll
+    for (int c = 0; c < CHUNKS; ++c) {
+      if (rt.template col<VEC>(c) < cols) {
+        uint64_t t[PAIRS];
+        unpack2<T>(raw[c], t);
+#pragma unroll
+        for (int i = 0; i < PAIRS; ++i) {
+          const uint64_t d = am::add2(t[i], nmu2);
+          v2 = am::fma2(d, d, v2);
+        }
+      }
+    }
+    const float var = row_reduce<CTA_ROW, false>(hsum2(v2), slot, phase) * inv_n;
     const float rs = rsqrtf(var + eps);
+    const uint64_t rs2 = splat2(rs);
     T* yr = y + row * cols;
 #pragma unroll
     for (int c = 0; c < CHUNKS; ++c) {
       const int col = rt.template col<VEC>(c);
       if (col < cols) {
-        float t[VEC], ws[VEC], bs[VEC];
-        unpack<T>(raw[c], t);
-        if (w) unpack<T>(ld_cached(w + col), ws);
-        if (b) unpack<T>(ld_cached(b + col), bs);
+        uint64_t t[PAIRS], ws[PAIRS], bs[PAIRS];
+        unpack2<T>(raw[c], t);
+        if (w) unpack2<T>(EARLY ? wraw[EARLY ? c : 0] : ld_cached(w + col), ws);
+        if (b) unpack2<T>(EARLY ? braw[EARLY ? c : 0] : ld_cached(b + col), bs);
 #pragma unroll
-        for (int i = 0; i < VEC; ++i) {
-          float o = (t[i] - mu) * rs;
-          if (w) o *= ws[i];
-          if (b) o += bs[i];
+        for (int i = 0; i < PAIRS; ++i) {
+          uint64_t o = am::mul2(am::add2(t[i], nmu2), rs2);
+          if (w) o = b ? am::fma2(o, ws[i], bs[i]) : am::mul2(o, ws[i]);
+          else if (b) o = am::add2(o, bs[i]);
           t[i] = o;
         }
-        st_stream(yr + col, pack<T>(t));
+        st_stream(yr + col, pack2<T>(t));
       }
     }
     if (rt.tid == 0) {
@@ -249,33 +270,58 @@ __global__ void __launch_bounds__(CTA_ROW ? 512 : 256, CTA_ROW ? 2 : 4)
   int phase = 0;
   RowThread<CTA_ROW> rt;
   for (int64_t row = rt.first_row(); row < rows; row += rt.row_step()) {
-    float xs[CHUNKS][VEC];
-    load_row<T, CHUNKS, CTA_ROW>(xs, x + row * row_stride, cols, rt);
+    constexpr bool EARLY = CHUNKS <= 4;  // as far as the registers allow
+    uint4 raw[CHUNKS], wraw[EARLY ? CHUNKS : 1];
+    const T* xr = x + row * row_stride;
+#pragma unroll
+    for (int c = 0; c < CHUNKS; ++c) {
+      const int col = rt.template col<VEC>(c);
+      raw[c] = col < cols ? ld_stream(xr + col) : make_uint4(0, 0, 0, 0);
+    }
+    // the weight is requested before the reduction: its latency hides behind the row's own load
+#pragma unroll
+    for (int c = 0; c < CHUNKS; ++c) {
+      const int col = rt.template col<VEC>(c);
+      if constexpr (EARLY) wraw[c] = col < cols ? ld_cached(w + col) : make_uint4(0, 0, 0, 0);
+    }
+    constexpr int PAIRS = VEC / 2;  // arithmetic on fp32 pairs (two-lane instructions)
+    uint64_t s2 = 0ull;
     float s = 0.f;
 #pragma unroll
     for (int c = 0; c < CHUNKS; ++c) {
       const int col = rt.template col<VEC>(c);
+      if (col + VEC <= partial) {
+        uint64_t t[PAIRS];
+        unpack2<T>(raw[c], t);
 #pragma unroll
-      for (int i = 0; i < VEC; ++i) s += (col + i < partial) ? xs[c][i] * xs[c][i] : 0.f;
+        for (int i = 0; i < PAIRS; ++i) s2 = am::fma2(t[i], t[i], s2);
+      } else if (col < partial) {
+        float t[VEC];
+        unpack<T>(raw[c], t);
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) s += (col + i < partial) ? t[i] * t[i] : 0.f;
+      }
     }
-    const float r = sqrtf(row_reduce<CTA_ROW, false>(s, slot, phase) / (float)partial);
+    const float r = sqrtf(row_reduce<CTA_ROW, false>(s + hsum2(s2), slot, phase) / (float)partial);
     const float inv = 1.f / (r + eps);
+    const uint64_t inv2 = splat2(inv);
+    T* yr = y + row * cols;
 #pragma unroll
     for (int c = 0; c < CHUNKS; ++c) {
       const int col = rt.template col<VEC>(c);
       if (col < cols) {
-        float ws[VEC], bs[VEC];
-        unpack<T>(ld_cached(w + col), ws);
-        if (b) unpack<T>(ld_cached(b + col), bs);
+        uint64_t t[PAIRS], ws[PAIRS], bs[PAIRS];
+        unpack2<T>(raw[c], t);
+        unpack2<T>(EARLY ? wraw[EARLY ? c : 0] : ld_cached(w + col), ws);
+        if (b) unpack2<T>(ld_cached(b + col), bs);
 #pragma unroll
-        for (int i = 0; i < VEC; ++i) {
-          float o = xs[c][i] * inv * ws[i];
-          if (b) o += bs[i];
-          xs[c][i] = o;
+        for (int i = 0; i < PAIRS; ++i) {
+          const uint64_t o = am::mul2(t[i], am::mul2(ws[i], inv2));
+          t[i] = b ? am::add2(o, bs[i]) : o;
         }
+        st_stream(yr + col, pack2<T>(t));
       }
     }
-    store_row<T, CHUNKS, CTA_ROW>(y + row * cols, xs, cols, rt);
     if (rt.tid == 0) rms[row] = r;
   }
 }
@@ -448,7 +494,7 @@ extern "C" int tb200_layer_norm_bwd(void* dx, void* dweight, void* dbias, const 
   {
     bool handled = false;
     int rc = try_layer_norm_bwd_grouped(dx, dweight, dbias, dy, x, weight, mean, rstd, workspace, workspace_bytes,
-                                        rows, cols, dtype, st, &handled);
+                                        rows, cols, dtype, st, &handled, /*allow_fused=*/true);
     if (rc || handled) return rc;
   }
   return dispatch_dtype(dtype, [&](auto tag) -> int {
@@ -673,7 +719,7 @@ extern "C" int tb200_layer_norm_bwd_static(void* dx, void* dweight, void* dbias,
     bool handled = false;
     int rc = try_layer_norm_bwd_grouped(dx, dweight, dbias, dy, x, weight, mean, rstd, scratch,
                                         LN_STATIC_SCRATCH_FLOATS * sizeof(float), rows, cols, dtype, st,
-                                        &handled);
+                                        &handled, /*allow_fused=*/false);
     if (rc || handled) return rc;
   }
   return dispatch_dtype(dtype, [&](auto tag) -> int {
@@ -738,152 +784,219 @@ __device__ inline void group_barrier(int group) {
   if constexpr (TPR > 32) asm volatile("bar.sync %0, %1;" ::"r"(group + 1), "n"(TPR) : "memory");
 }
 
-// Sums two values over the TPR threads of a group. `slots` holds [2 phases][16 warps][2].
-template <int TPR>
-__device__ inline void group_sum2(float& a, float& b, float* slots, int& phase, int group) {
+// Sums NV (1 or 2) values over the TPR threads of a group. `slots` holds [2 phases][16 warps][2];
+// the per-warp sums are read back with 16-byte loads.
+template <int TPR, int NV>
+__device__ inline void group_sum(float& a, float& b, float* slots, int& phase, int group) {
   a = warp_sum(a);
-  b = warp_sum(b);
+  if constexpr (NV == 2) b = warp_sum(b);
   if constexpr (TPR > 32) {
-    constexpr int WPG = TPR / 32;  // warps per group
+    constexpr int WPG = TPR / 32;  // warps per group: 2, 4, 8 or 16
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     float* s = slots + phase * 32;
     phase ^= 1;
-    if (lane == 0) {
-      s[warp * 2] = a;
-      s[warp * 2 + 1] = b;
-    }
-    group_barrier<TPR>(group);
-    const int w0 = group * WPG;
-    float ra = 0.f, rb = 0.f;
+    if constexpr (NV == 2) {
+      if (lane == 0) *reinterpret_cast<float2*>(s + warp * 2) = make_float2(a, b);
+      group_barrier<TPR>(group);
+      const float4* v = reinterpret_cast<const float4*>(s + group * WPG * 2);
+      float ra = 0.f, rb = 0.f;
 #pragma unroll
-    for (int w = 0; w < WPG; ++w) {
-      ra += s[(w0 + w) * 2];
-      rb += s[(w0 + w) * 2 + 1];
+      for (int w = 0; w < WPG / 2; ++w) {
+        const float4 t = v[w];
+        ra += t.x + t.z;
+        rb += t.y + t.w;
+      }
+      a = ra;
+      b = rb;
+    } else {
+      if (lane == 0) s[warp] = a;
+      group_barrier<TPR>(group);
+      float ra = 0.f;
+      if constexpr (WPG >= 4) {
+        const float4* v = reinterpret_cast<const float4*>(s + group * WPG);
+#pragma unroll
+        for (int w = 0; w < WPG / 4; ++w) {
+          const float4 t = v[w];
+          ra += (t.x + t.y) + (t.z + t.w);
+        }
+      } else {
+        const float2 t = *reinterpret_cast<const float2*>(s + group * WPG);
+        ra = t.x + t.y;
+      }
+      a = ra;
     }
-    a = ra;
-    b = rb;
   }
 }
 
-template <typename T, int CHUNKS, int TPR, bool RMS, bool WANT_B>
-__global__ void __launch_bounds__(512, 2)
+// DEPTH rows are in flight per group: a group requests the rows up to DEPTH-1 iterations
+// ahead before it works on the current one (a ring of register buffers, the loop unrolled over
+// the ring so that no register is copied).
+template <typename T, int CHUNKS, int TPR, bool RMS, bool WANT_B, int DEPTH, int MINB>
+__global__ void __launch_bounds__(512, MINB)
     norm_bwd_grouped(T* __restrict__ dx, float* __restrict__ partial, const T* __restrict__ dy,
                      const T* __restrict__ x, const T* __restrict__ w, const float* __restrict__ stat_a,
                      const float* __restrict__ stat_b, int64_t rows, int cols, int64_t x_row_stride,
-                     int partial_cols, float eps, int want_cols) {
+                     int partial_cols, float eps, int want_cols, T* __restrict__ dw_out,
+                     T* __restrict__ db_out, int fused_slab) {
   constexpr int VEC = Traits<T>::VEC;
   constexpr int GROUPS = 512 / TPR;
   extern __shared__ __align__(16) float colbuf[];  // [2][cols], used after the row loop
-  __shared__ float slots[64];
+  __shared__ __align__(16) float slots[64];
   int phase = 0;
   const int group = threadIdx.x / TPR, tid = threadIdx.x % TPR;
   const float inv_n = 1.f / (float)cols;
-  // The row (x and dy) stays packed in registers as loaded and is unpacked once per pass; the
-  // weights are re-read per pass (L1 hits). Live state per thread: two packed rows and the
-  // fp32 column accumulators.
-  float acc_w[CHUNKS][VEC], acc_b[WANT_B ? CHUNKS : 1][VEC];
+  // A row (x and dy) stays packed in registers as loaded and is unpacked once per pass. A
+  // thread always works on the same columns, so with one vector per thread its weights are
+  // loaded once, packed; with two they are re-read per pass (L1 hits).
+  constexpr bool W_REGS = CHUNKS == 1 || MINB == 1;
+  constexpr int PAIRS = VEC / 2;  // arithmetic runs on fp32 pairs (two-lane instructions)
+  uint64_t acc_w[CHUNKS][PAIRS], acc_b[WANT_B ? CHUNKS : 1][PAIRS];
+  uint4 wreg[CHUNKS];
 #pragma unroll
-  for (int c = 0; c < CHUNKS; ++c)
+  for (int c = 0; c < CHUNKS; ++c) {
+    const int col = (c * TPR + tid) * VEC;
+    wreg[c] = (W_REGS && w && col < cols) ? ld_cached(w + col) : make_uint4(0, 0, 0, 0);
 #pragma unroll
-    for (int i = 0; i < VEC; ++i) {
-      acc_w[c][i] = 0.f;
-      if constexpr (WANT_B) acc_b[c][i] = 0.f;
+    for (int i = 0; i < PAIRS; ++i) {
+      acc_w[c][i] = 0ull;
+      if constexpr (WANT_B) acc_b[c][i] = 0ull;
     }
-  auto load_w = [&](float (&dst)[VEC], int col) {
-    if (w && col < cols) {
-      unpack<T>(ld_cached(w + col), dst);
+  }
+  const bool has_w = w != nullptr;
+  auto get_w = [&](uint64_t (&dst)[PAIRS], int c) {
+    const int col = (c * TPR + tid) * VEC;
+    if (has_w && (W_REGS || col < cols)) {
+      // out-of-range columns: zeros, and dy is zero there as well
+      unpack2<T>(W_REGS ? wreg[c] : ld_cached(w + col), dst);
     } else {
 #pragma unroll
-      for (int i = 0; i < VEC; ++i) dst[i] = 1.f;  // out-of-range columns carry dy = 0
+      for (int i = 0; i < PAIRS; ++i) dst[i] = splat2(1.f);
     }
   };
-  // every group runs the same number of iterations (the group barrier needs all its threads,
-  // and out-of-range rows are simply predicated off)
-  const int64_t row_step = (int64_t)gridDim.x * GROUPS;
-  for (int64_t row0 = (int64_t)blockIdx.x * GROUPS; row0 < rows; row0 += row_step) {
-    const int64_t row = row0 + group;
-    const bool live = row < rows;
-    uint4 rx[CHUNKS], rg[CHUNKS];
-#pragma unroll
-    for (int c = 0; c < CHUNKS; ++c) {
-      const int col = (c * TPR + tid) * VEC;
-      if (live && col < cols) {
-        rx[c] = ld_stream(x + row * x_row_stride + col);
-        rg[c] = ld_stream(dy + row * cols + col);
-      } else {
-        rx[c] = make_uint4(0, 0, 0, 0);
-        rg[c] = make_uint4(0, 0, 0, 0);
-      }
-    }
-    const float sa = live ? stat_a[row] : 0.f;
-    const float sb = (!RMS && live) ? stat_b[row] : 0.f;
-    if constexpr (!RMS) {
-      // LayerNorm: sa = mean, sb = rstd
-      float s1 = 0.f, s2 = 0.f;
+  struct RowRegs {
+    uint4 x[CHUNKS], g[CHUNKS];
+    float sa, sb;
+  };
+  auto request = [&](RowRegs& r, int64_t row) {
+    if (row < rows) {
 #pragma unroll
       for (int c = 0; c < CHUNKS; ++c) {
         const int col = (c * TPR + tid) * VEC;
-        const bool in = live && col < cols;
-        float xs[VEC], gs[VEC], wv[VEC];
-        unpack<T>(rx[c], xs);
-        unpack<T>(rg[c], gs);
-        load_w(wv, col);
-#pragma unroll
-        for (int i = 0; i < VEC; ++i) {
-          const float xh = in ? (xs[i] - sa) * sb : 0.f;
-          const float d = gs[i];
-          acc_w[c][i] += d * xh;
-          if constexpr (WANT_B) acc_b[c][i] += d;
-          const float g = d * wv[i];
-          s1 += g * xh;
-          s2 += g;
+        if (col < cols) {
+          r.x[c] = ld_stream(x + row * x_row_stride + col);
+          r.g[c] = ld_stream(dy + row * cols + col);
+        } else {
+          r.x[c] = make_uint4(0, 0, 0, 0);
+          r.g[c] = make_uint4(0, 0, 0, 0);
         }
       }
-      group_sum2<TPR>(s1, s2, slots, phase, group);
-      const float c1 = s1 * inv_n, c2 = s2 * inv_n;
+      r.sa = __ldg(stat_a + row);
+      r.sb = RMS ? 0.f : __ldg(stat_b + row);
+    }
+  };
+  auto process = [&](const RowRegs& r, int64_t row) {
+    const float sa = r.sa, sb = r.sb;
+    if constexpr (!RMS) {
+      // LayerNorm: sa = mean, sb = rstd; xh = (x - mean) * rstd.
+      // Out-of-range columns hold x = dy = 0: their xh is finite and every product with dy is 0.
+      const uint64_t nsa2 = splat2(-sa), sb2 = splat2(sb);
+      uint64_t s1 = 0ull, s2 = 0ull;
+#pragma unroll
+      for (int c = 0; c < CHUNKS; ++c) {
+        uint64_t xs[PAIRS], gs[PAIRS], wv[PAIRS];
+        unpack2<T>(r.x[c], xs);
+        unpack2<T>(r.g[c], gs);
+        get_w(wv, c);
+#pragma unroll
+        for (int i = 0; i < PAIRS; ++i) {
+          const uint64_t xh = am::mul2(am::add2(xs[i], nsa2), sb2);
+          acc_w[c][i] = am::fma2(gs[i], xh, acc_w[c][i]);
+          if constexpr (WANT_B) acc_b[c][i] = am::add2(acc_b[c][i], gs[i]);
+          const uint64_t g = am::mul2(gs[i], wv[i]);
+          s1 = am::fma2(g, xh, s1);
+          s2 = am::add2(s2, g);
+        }
+      }
+      float t1 = hsum2(s1), t2 = hsum2(s2);
+      group_sum<TPR, 2>(t1, t2, slots, phase, group);
+      // dx = rstd * (g - xh * c1 - c2) with g = dy * w, c1 = mean(g * xh), c2 = mean(g)
+      const uint64_t k1 = splat2(-sb * t1 * inv_n), k2 = splat2(-sb * t2 * inv_n);
 #pragma unroll
       for (int c = 0; c < CHUNKS; ++c) {
         const int col = (c * TPR + tid) * VEC;
-        float xs[VEC], gs[VEC], wv[VEC];
-        unpack<T>(rx[c], xs);
-        unpack<T>(rg[c], gs);
-        load_w(wv, col);
+        uint64_t xs[PAIRS], gs[PAIRS], wv[PAIRS];
+        unpack2<T>(r.x[c], xs);
+        unpack2<T>(r.g[c], gs);
+        get_w(wv, c);
 #pragma unroll
-        for (int i = 0; i < VEC; ++i) xs[i] = sb * (gs[i] * wv[i] - (xs[i] - sa) * sb * c1 - c2);
-        if (live && col < cols) st_stream(dx + row * cols + col, pack<T>(xs));
+        for (int i = 0; i < PAIRS; ++i) {
+          const uint64_t xh = am::mul2(am::add2(xs[i], nsa2), sb2);
+          xs[i] = am::fma2(am::mul2(gs[i], wv[i]), sb2, am::fma2(xh, k1, k2));
+        }
+        if (col < cols) st_stream(dx + row * cols + col, pack2<T>(xs));
       }
     } else {
       // RMSNorm: sa = rms
-      const float inv = live ? 1.f / (sa + eps) : 0.f;
-      float s = 0.f, unused = 0.f;
+      const float inv = 1.f / (sa + eps);
+      const uint64_t inv2 = splat2(inv);
+      uint64_t s = 0ull;
 #pragma unroll
       for (int c = 0; c < CHUNKS; ++c) {
-        const int col = (c * TPR + tid) * VEC;
-        float xs[VEC], gs[VEC], wv[VEC];
-        unpack<T>(rx[c], xs);
-        unpack<T>(rg[c], gs);
-        load_w(wv, col);
+        uint64_t xs[PAIRS], gs[PAIRS], wv[PAIRS];
+        unpack2<T>(r.x[c], xs);
+        unpack2<T>(r.g[c], gs);
+        get_w(wv, c);
 #pragma unroll
-        for (int i = 0; i < VEC; ++i) {
-          const float d = gs[i];
-          acc_w[c][i] += d * xs[i] * inv;
-          if constexpr (WANT_B) acc_b[c][i] += d;
-          s += d * wv[i] * xs[i];
+        for (int i = 0; i < PAIRS; ++i) {
+          const uint64_t t = am::mul2(gs[i], xs[i]);
+          acc_w[c][i] = am::fma2(t, inv2, acc_w[c][i]);
+          if constexpr (WANT_B) acc_b[c][i] = am::add2(acc_b[c][i], gs[i]);
+          s = am::fma2(t, wv[i], s);
         }
       }
-      group_sum2<TPR>(s, unused, slots, phase, group);
-      const float k = sa > 0.f ? s * inv * inv / ((float)partial_cols * sa) : 0.f;
+      float t1 = hsum2(s), unused = 0.f;
+      group_sum<TPR, 1>(t1, unused, slots, phase, group);
+      const float k = sa > 0.f ? t1 * inv * inv / ((float)partial_cols * sa) : 0.f;
+      const uint64_t nk2 = splat2(-k);
 #pragma unroll
       for (int c = 0; c < CHUNKS; ++c) {
         const int col = (c * TPR + tid) * VEC;
-        float xs[VEC], gs[VEC], wv[VEC];
-        unpack<T>(rx[c], xs);
-        unpack<T>(rg[c], gs);
-        load_w(wv, col);
+        uint64_t xs[PAIRS], gs[PAIRS], wv[PAIRS];
+        unpack2<T>(r.x[c], xs);
+        unpack2<T>(r.g[c], gs);
+        get_w(wv, c);
+        if (col + VEC <= partial_cols) {
 #pragma unroll
-        for (int i = 0; i < VEC; ++i)
-          xs[i] = gs[i] * wv[i] * inv - ((col + i < partial_cols) ? xs[i] * k : 0.f);
-        if (live && col < cols) st_stream(dx + row * cols + col, pack<T>(xs));
+          for (int i = 0; i < PAIRS; ++i)
+            xs[i] = am::fma2(gs[i], am::mul2(wv[i], inv2), am::mul2(xs[i], nk2));
+        } else {
+#pragma unroll
+          for (int i = 0; i < PAIRS; ++i) {
+            float x0, x1;
+            am::unpack2f(xs[i], x0, x1);
+            const uint64_t xk = am::pack2f(col + 2 * i < partial_cols ? -k * x0 : 0.f,
+                                           col + 2 * i + 1 < partial_cols ? -k * x1 : 0.f);
+            xs[i] = am::fma2(gs[i], am::mul2(wv[i], inv2), xk);
+          }
+        }
+        if (col < cols) st_stream(dx + row * cols + col, pack2<T>(xs));
+      }
+    }
+  };
+  // Each group walks its own rows (the group barrier only involves the group's threads, and
+  // the trip count is uniform within a group).
+  const int64_t row_step = (int64_t)gridDim.x * GROUPS;
+  int64_t row = (int64_t)blockIdx.x * GROUPS + group;
+  RowRegs ring[DEPTH];
+#pragma unroll
+  for (int d = 0; d + 1 < DEPTH; ++d) request(ring[d], row + d * row_step);
+  while (row < rows) {
+#pragma unroll
+    for (int k = 0; k < DEPTH; ++k) {
+      if (row < rows) {
+        request(ring[(k + DEPTH - 1) % DEPTH], row + (DEPTH - 1) * row_step);
+        process(ring[k], row);
+        row += row_step;
       }
     }
   }
@@ -897,13 +1010,15 @@ __global__ void __launch_bounds__(512, 2)
           if (col < cols) {
 #pragma unroll
             for (int i = 0; i < VEC; ++i) {
-              const float bv = WANT_B ? acc_b[WANT_B ? c : 0][i] : 0.f;
+              float pw[2], pb[2] = {0.f, 0.f};
+              am::unpack2f(acc_w[c][i >> 1], pw[0], pw[1]);
+              if constexpr (WANT_B) am::unpack2f(acc_b[c][i >> 1], pb[0], pb[1]);
               if (g == 0) {
-                colbuf[col + i] = acc_w[c][i];
-                colbuf[cols + col + i] = bv;
+                colbuf[col + i] = pw[i & 1];
+                colbuf[cols + col + i] = pb[i & 1];
               } else {
-                colbuf[col + i] += acc_w[c][i];
-                colbuf[cols + col + i] += bv;
+                colbuf[col + i] += pw[i & 1];
+                colbuf[cols + col + i] += pb[i & 1];
               }
             }
           }
@@ -915,49 +1030,97 @@ __global__ void __launch_bounds__(512, 2)
     for (int i = threadIdx.x * 4; i < 2 * cols; i += 512 * 4)
       *reinterpret_cast<float4*>(out + i) = *reinterpret_cast<const float4*>(colbuf + i);
   }
+  if (fused_slab > 0) {
+    // Cooperative launch: after a grid-wide barrier the CTAs share the column sums of the
+    // partial rows among themselves, `fused_slab` adjacent columns of the flattened [2][cols]
+    // row per CTA and step, 512 / fused_slab threads walking the partial rows of each column.
+    // The summation order is fixed, so the result does not depend on scheduling.
+    cooperative_groups::this_grid().sync();
+    __shared__ float red[512];
+    const int nparts = gridDim.x;
+    const int lanes = 512 / fused_slab;
+    const int cl = threadIdx.x % fused_slab, j = threadIdx.x / fused_slab;
+    const int limit = db_out ? 2 * cols : cols;
+    for (int base = blockIdx.x * fused_slab; base < limit; base += gridDim.x * fused_slab) {
+      const int cc = base + cl;
+      float acc = 0.f;
+      if (cc < limit) {
+        for (int p0 = j; p0 < nparts; p0 += lanes * 8) {
+          float v[8];
+#pragma unroll
+          for (int u = 0; u < 8; ++u) {
+            const int p = p0 + lanes * u;
+            v[u] = p < nparts ? __ldcg(partial + (int64_t)p * 2 * cols + cc) : 0.f;
+          }
+#pragma unroll
+          for (int u = 0; u < 8; ++u) acc += v[u];
+        }
+      }
+      red[j * fused_slab + cl] = acc;
+      __syncthreads();
+      if (threadIdx.x < fused_slab && cc < limit) {
+        float sum = 0.f;
+        for (int jj = 0; jj < lanes; ++jj) sum += red[jj * fused_slab + cl];
+        T* o = cc < cols ? dw_out : db_out;
+        if (o) o[cc < cols ? cc : cc - cols] = Traits<T>::from_f(sum);
+      }
+      __syncthreads();
+    }
+  }
 }
 
 struct GroupedPlan {
   bool ok = false;
-  int tpr = 32, chunks = 1;
+  int tpr = 32, chunks = 1, depth = 1, minb = 2;
 };
 
-// `two_per_thread_16bit`: 16-bit rows may put two vectors on a thread. That fits the
-// 64-register budget only when a single column accumulator is kept (RMSNorm without bias
-// gradient: measured 57 us against 61 us on bf16 [8192, 4096]); with both accumulators it
-// spills and is slower (LayerNorm: 89 us against 59 us), so those cases keep one vector.
+// Plan of the grouped kernel, from measurements on bf16 [8192, 4096] and fp32 [4096, 1024]:
+// rows of up to 256 vectors put one vector on a thread, two CTAs per SM (64 registers) and
+// request one row ahead (none for 16-bit rows with a bias gradient, whose second set of
+// accumulators leaves no registers for it); wider rows put two vectors on a thread, one CTA
+// per SM (128 registers), one row ahead. Fat threads matter because the kernel is close to
+// issue-bound: the per-row overhead (addresses, shuffles, barrier) is paid per thread.
 template <typename T>
-static GroupedPlan plan_grouped(int64_t cols, bool ptrs_ok, bool two_per_thread_16bit) {
+static GroupedPlan plan_grouped(int64_t cols, bool ptrs_ok, bool want_b) {
   GroupedPlan p;
   constexpr int VEC = Traits<T>::VEC;
   if (!ptrs_ok || cols <= 0 || cols % VEC != 0) return p;
   const int64_t vecs = cols / VEC;
-  // 16-bit rows keep one vector (8 elements) per thread when they fit 512 threads: two vectors
-  // per thread do not fit the 64-register budget of two resident CTAs without spilling
-  const int per_thread = (sizeof(T) == 2 && vecs <= 512 && !two_per_thread_16bit) ? 1 : 2;
-  for (int tpr : {32, 128, 256, 512}) {
-    if ((int64_t)tpr * per_thread >= vecs) {
-      p.ok = true;
-      p.tpr = tpr;
-      p.chunks = vecs > tpr ? 2 : 1;
-      return p;
-    }
+  if (vecs > 1024) return p;
+  p.ok = true;
+  if (vecs <= 256) {
+    p.tpr = vecs <= 32 ? 32 : vecs <= 128 ? 128 : 256;
+    p.chunks = 1;
+    p.depth = (sizeof(T) == 2 && want_b) ? 1 : 2;
+    p.minb = 2;
+  } else {
+    p.tpr = vecs <= 512 ? 256 : 512;
+    p.chunks = 2;
+    p.depth = 2;
+    p.minb = 1;
   }
   return p;
 }
 
+static int g_norm_fused_finalize = 1;
+
 // Launches the grouped kernel; returns the number of partial rows written (the grid size) in
 // *nparts. `grid_cap` bounds the grid (the workspace of the caller must hold that many rows).
+// With `fuse` the launch is cooperative and the kernel also folds the partial rows into
+// dw_out/db_out after a grid barrier; *fused reports whether that happened (when the grid
+// cannot be co-resident the plain launch is used and the caller runs the finalize kernel).
 template <typename T, bool RMS, bool WANT_B>
 static int launch_grouped(const GroupedPlan& gp, T* dx, float* partial, const T* dy, const T* x, const T* w,
                           const float* stat_a, const float* stat_b, int64_t rows, int64_t cols,
                           int64_t x_row_stride, int64_t partial_cols, float eps, bool want_cols,
-                          int64_t grid_cap, int* nparts, cudaStream_t st) {
+                          int64_t grid_cap, int* nparts, cudaStream_t st, bool fuse = false, T* dw_out = nullptr,
+                          T* db_out = nullptr, bool* fused = nullptr) {
   const int groups = 512 / gp.tpr;
   int64_t grid = ceil_div(rows, groups);
   if (grid > grid_cap) grid = grid_cap;
   if (grid < 1) grid = 1;
   *nparts = (int)grid;
+  if (fused) *fused = false;
   const size_t smem = want_cols ? (size_t)2 * cols * sizeof(float) : 0;
   auto go = [&](auto kern) -> int {
     if (smem > 48 * 1024) {
@@ -967,20 +1130,46 @@ static int launch_grouped(const GroupedPlan& gp, T* dx, float* partial, const T*
         return (int)e;
       }
     }
-    kern<<<(unsigned)grid, 512, smem, st>>>(dx, partial, dy, x, w, stat_a, stat_b, rows, (int)cols, x_row_stride,
-                                            (int)partial_cols, eps, want_cols ? 1 : 0);
+    int cols_i = (int)cols, pc_i = (int)partial_cols, wc_i = want_cols ? 1 : 0, slab = 0;
+    if (fuse && want_cols && g_norm_fused_finalize) {
+      int per_sm = 0;
+      if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, 512, smem) == cudaSuccess &&
+          (int64_t)per_sm * sm_count() >= grid) {
+        const int64_t limit = db_out ? 2 * cols : cols;
+        slab = 16;
+        while (slab < 64 && ceil_div(limit, slab) > grid) slab *= 2;
+      }
+    }
+    if (slab > 0) {
+      void* args[] = {&dx, &partial, &dy, &x, &w, &stat_a, &stat_b, &rows, &cols_i, &x_row_stride,
+                      &pc_i, &eps, &wc_i, &dw_out, &db_out, &slab};
+      cudaError_t e = cudaLaunchCooperativeKernel((const void*)kern, dim3((unsigned)grid), dim3(512), args, smem, st);
+      if (e == cudaSuccess) {
+        if (fused) *fused = true;
+        return launch_status("norm_bwd_grouped");
+      }
+      (void)cudaGetLastError();  // fall through to the plain launch
+      slab = 0;
+    }
+    kern<<<(unsigned)grid, 512, smem, st>>>(dx, partial, dy, x, w, stat_a, stat_b, rows, cols_i, x_row_stride, pc_i,
+                                            eps, wc_i, (T*)nullptr, (T*)nullptr, 0);
     return launch_status("norm_bwd_grouped");
   };
-  switch (gp.tpr * 10 + gp.chunks) {
-    case 321: return go(norm_bwd_grouped<T, 1, 32, RMS, WANT_B>);
-    case 322: return go(norm_bwd_grouped<T, 2, 32, RMS, WANT_B>);
-    case 1281: return go(norm_bwd_grouped<T, 1, 128, RMS, WANT_B>);
-    case 1282: return go(norm_bwd_grouped<T, 2, 128, RMS, WANT_B>);
-    case 2561: return go(norm_bwd_grouped<T, 1, 256, RMS, WANT_B>);
-    case 2562: return go(norm_bwd_grouped<T, 2, 256, RMS, WANT_B>);
-    case 5121: return go(norm_bwd_grouped<T, 1, 512, RMS, WANT_B>);
-    case 5122: return go(norm_bwd_grouped<T, 2, 512, RMS, WANT_B>);
+#define TB200_GROUPED_CASE(C, R, D, M)                                                      \
+  if (gp.chunks == C && gp.tpr == R && gp.depth == D && gp.minb == M)                       \
+    return go(norm_bwd_grouped<T, C, R, RMS, WANT_B, D, M>);
+  if constexpr (sizeof(T) == 2 && WANT_B) {
+    TB200_GROUPED_CASE(1, 32, 1, 2)
+    TB200_GROUPED_CASE(1, 128, 1, 2)
+    TB200_GROUPED_CASE(1, 256, 1, 2)
+  } else {
+    TB200_GROUPED_CASE(1, 32, 2, 2)
+    TB200_GROUPED_CASE(1, 128, 2, 2)
+    TB200_GROUPED_CASE(1, 256, 2, 2)
   }
+  TB200_GROUPED_CASE(2, 256, 2, 1)
+  TB200_GROUPED_CASE(2, 512, 2, 1)
+#undef TB200_GROUPED_CASE
   set_error("internal: bad grouped plan");
   return TB200_ERR_INVALID;
 }
@@ -988,30 +1177,32 @@ static int launch_grouped(const GroupedPlan& gp, T* dx, float* partial, const T*
 int try_layer_norm_bwd_grouped(void* dx, void* dweight, void* dbias, const void* dy, const void* x,
                                const void* weight, const float* mean, const float* rstd, void* workspace,
                                size_t workspace_bytes, int64_t rows, int64_t cols, int dtype, cudaStream_t st,
-                               bool* handled) {
+                               bool* handled, bool allow_fused) {
   *handled = false;
   const bool want_cols = dweight || dbias;
   return dispatch_dtype(dtype, [&](auto tag) -> int {
     using T = decltype(tag);
     const bool ok = aligned16(dx) && aligned16(dy) && aligned16(x) && (!weight || aligned16(weight)) &&
                     (!want_cols || (workspace && aligned16(workspace))) && rows > 0;
-    GroupedPlan gp = plan_grouped<T>(cols, ok, false);
+    GroupedPlan gp = plan_grouped<T>(cols, ok, true);
     if (!gp.ok) return 0;
-    int64_t cap = (int64_t)sm_count() * 2;
+    int64_t cap = (int64_t)sm_count() * gp.minb;
     if (want_cols) {
       const int64_t fit = (int64_t)(workspace_bytes / ((size_t)2 * cols * sizeof(float)));
       if (fit < 1) return 0;
       if (cap > fit) cap = fit;
     }
     int nparts = 0;
+    bool fused = false;
     int rc = launch_grouped<T, false, true>(gp, (T*)dx, (float*)workspace, (const T*)dy, (const T*)x, (const T*)weight,
-                                      mean, rstd, rows, cols, cols, cols, 0.f, want_cols, cap, &nparts, st);
+                                      mean, rstd, rows, cols, cols, cols, 0.f, want_cols, cap, &nparts, st,
+                                      allow_fused, (T*)dweight, (T*)dbias, &fused);
     if (rc) return rc;
-    if (want_cols) {
+    if (want_cols && !fused) {
       rc = finalize_cols<T>((T*)dweight, (T*)dbias, (const float*)workspace, nparts, cols, st);
       if (rc) return rc;
     }
-    note_kernel("row_vec", want_cols ? 2 : 1);
+    note_kernel("row_vec", want_cols && !fused ? 2 : 1);
     *handled = true;
     return 0;
   });
@@ -1027,26 +1218,37 @@ int try_rms_norm_bwd_grouped(void* dx, void* dweight, void* dbias, const void* d
     constexpr int VEC = Traits<T>::VEC;
     const bool ok = aligned16(dx) && aligned16(dy) && aligned16(x) && aligned16(weight) && col_stride == 1 &&
                     row_stride % VEC == 0 && row_stride >= cols && workspace && aligned16(workspace) && rows > 0;
-    GroupedPlan gp = plan_grouped<T>(cols, ok, dbias == nullptr);
+    GroupedPlan gp = plan_grouped<T>(cols, ok, dbias != nullptr);
     if (!gp.ok) return 0;
-    int64_t cap = (int64_t)sm_count() * 2;
+    int64_t cap = (int64_t)sm_count() * gp.minb;
     const int64_t fit = (int64_t)(workspace_bytes / ((size_t)2 * cols * sizeof(float)));
     if (fit < 1) return 0;
     if (cap > fit) cap = fit;
     int nparts = 0;
+    bool fused = false;
     int rc = dbias ? launch_grouped<T, true, true>(gp, (T*)dx, (float*)workspace, (const T*)dy, (const T*)x,
                                                    (const T*)weight, rms, nullptr, rows, cols, row_stride,
-                                                   partial_cols, eps, true, cap, &nparts, st)
+                                                   partial_cols, eps, true, cap, &nparts, st, true, (T*)dweight,
+                                                   (T*)dbias, &fused)
                    : launch_grouped<T, true, false>(gp, (T*)dx, (float*)workspace, (const T*)dy, (const T*)x,
                                                     (const T*)weight, rms, nullptr, rows, cols, row_stride,
-                                                    partial_cols, eps, true, cap, &nparts, st);
+                                                    partial_cols, eps, true, cap, &nparts, st, true, (T*)dweight,
+                                                    (T*)dbias, &fused);
     if (rc) return rc;
-    rc = finalize_cols<T>((T*)dweight, (T*)dbias, (const float*)workspace, nparts, cols, st);
-    if (rc) return rc;
-    note_kernel("row_vec", 2);
+    if (!fused) {
+      rc = finalize_cols<T>((T*)dweight, (T*)dbias, (const float*)workspace, nparts, cols, st);
+      if (rc) return rc;
+    }
+    note_kernel("row_vec", fused ? 1 : 2);
     *handled = true;
     return 0;
   });
 }
 
 }  // namespace tb200
+
+extern "C" int tb200_set_norm_fused_finalize(int on) {
+  const int old = tb200::g_norm_fused_finalize;
+  tb200::g_norm_fused_finalize = on;
+  return old;
+}
