@@ -44,7 +44,12 @@ bool make_tensor_map_bhsd(CUtensorMap* map, const void* base, int64_t B, int64_t
 
 namespace {
 
-constexpr int BWD_THREADS = 512;
+// Warps: 0 producer, 1 MMA issuer, 2 tensor-memory allocation, 3 idle, then 4 * CG compute
+// warps (a key row is shared by CG threads, each taking 128 / CG query columns) and four drain
+// warps. CG is 2, except for the masked kernel at D = 64, where the compute warps are the
+// critical path (one shared-memory load per mask element) and CG = 4 halves their work.
+__host__ __device__ constexpr int cgroups_for(int D, bool masked) { return (masked && D == 64) ? 4 : 2; }
+__host__ __device__ constexpr int bwd_threads_for(int D, bool masked) { return (4 + 4 * cgroups_for(D, masked) + 4) * 32; }
 constexpr float LOG2E = 1.4426950408889634f;
 
 struct BwdParams {
@@ -79,12 +84,6 @@ __device__ inline void bulk_load(void* smem_dst, const void* gsrc, uint32_t byte
 }
 // Adds a [128 rows][32 floats] shared-memory box (128-byte swizzled) into a 2-D fp32 tensor.
 __device__ inline void tma_reduce_add_2d(const CUtensorMap* map, const void* smem_src, int x, int y) {
-#ifdef TB200_EXPERIMENT_PLAIN_STORE
-  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%1, %2}], [%3];" ::"l"(map),
-               "r"(x), "r"(y), "r"(ptx::smem_u32(smem_src))
-               : "memory");
-  return;
-#endif
   asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%1, %2}], [%3];" ::"l"(map),
                "r"(x), "r"(y), "r"(ptx::smem_u32(smem_src))
                : "memory");
@@ -109,12 +108,27 @@ __device__ inline void unpack_pair<__half>(uint32_t v, float& lo, float& hi) {
   hi = f.y;
 }
 
+#ifdef TB200_ATTN_PROFILE
+__device__ long long g_prof[64];
+#define PROF_DECL long long prof_acc[12] = {0}; long long prof_last = clock64(); const bool prof_on = blockIdx.x == 0 && blockIdx.y == 0;
+#define PROF(slot) do { if (prof_on) { long long t_ = clock64(); prof_acc[slot] += t_ - prof_last; prof_last = t_; } } while (0)
+#define PROF_FLUSH(role) do { if (prof_on) for (int i_ = 0; i_ < 12; ++i_) g_prof[(role) * 16 + i_] = prof_acc[i_]; } while (0)
+#else
+#define PROF_DECL
+#define PROF(slot)
+#define PROF_FLUSH(role)
+#endif
+
 template <typename T, int D, bool CAUSAL, bool MASKED>
-__global__ void __launch_bounds__(BWD_THREADS, 1)
+__global__ void __launch_bounds__(bwd_threads_for(D, MASKED), 1)
     attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                        const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do,
                        const __grid_constant__ CUtensorMap map_dq, const __grid_constant__ CUtensorMap map_mask,
                        const BwdParams p) {
+  constexpr int CGROUPS = cgroups_for(D, MASKED);
+  constexpr int NCH = 4 / CGROUPS;  // 32-column chunks per compute thread
+  constexpr int COMPUTE_WARPS = 4 * CGROUPS;
+  constexpr int DRAIN_WARP0 = 4 + COMPUTE_WARPS;
   constexpr int TILE_BYTES = 128 * D * 2;
   constexpr int NBOX = D / 64;
   constexpr int BOX_BYTES = 128 * 64 * 2;
@@ -148,8 +162,9 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
   uint8_t* do_smem = smem + 4 * TILE_BYTES;   // [2]
   uint8_t* ds_smem = smem + 6 * TILE_BYTES;
   uint8_t* mask_smem = smem + 6 * TILE_BYTES + DS_BYTES;  // [2][MASK_TILE_BYTES] when MASK_SMEM
-  float* nlse_smem =
-      reinterpret_cast<float*>(smem + 6 * TILE_BYTES + DS_BYTES + (MASK_SMEM ? 2 * MASK_TILE_BYTES : 0));  // [2][128]
+  constexpr int STAGE_BYTES = DQ_T ? 0 : 128 * D * 4;  // dQ staging tile (fp32), D = 64 only
+  uint8_t* dq_stage = smem + 6 * TILE_BYTES + DS_BYTES + (MASK_SMEM ? 2 * MASK_TILE_BYTES : 0);
+  float* nlse_smem = reinterpret_cast<float*>(dq_stage + STAGE_BYTES);  // [2][128]
   float* ndelta_smem = nlse_smem + 256;                                           // [2][128]
   uint64_t* bars = reinterpret_cast<uint64_t*>(ndelta_smem + 256);
   uint64_t* kv_full = bars + 0;
@@ -166,14 +181,20 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int jt = blockIdx.x;  // key/value tile; under the causal mask the first tiles do most work
-  const int bh = blockIdx.y;
+  int jt = blockIdx.x;
+  int bh = blockIdx.y;
+  if (MASKED && p.a.ms[1] == 0 && p.a.H > 1) {
+    const int lin = (int)blockIdx.x + (int)gridDim.x * (int)blockIdx.y;
+    const int rest = lin / (int)p.a.H;
+    jt = rest % (int)gridDim.x;
+    bh = (rest / (int)gridDim.x) * (int)p.a.H + lin % (int)p.a.H;
+  }
   const int b = bh / (int)p.a.H, h = bh % (int)p.a.H;
   const int i_begin = CAUSAL ? jt : 0;
   const int steps = p.nq - i_begin;
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < 12; ++i) ptx::mbar_init(&bars[i], (i == 6 || i == 8) ? 256 : (i == 10 ? 128 : 1));
+    for (int i = 0; i < 12; ++i) ptx::mbar_init(&bars[i], (i == 6 || i == 8) ? COMPUTE_WARPS * 32 : (i == 10 ? 128 : 1));
     *abort_flag = 0;
     if ((ptx::smem_u32(smem) & 1023u) != 0) {  // swizzled tiles need a 1024-byte aligned base
       *abort_flag = 1;
@@ -242,6 +263,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
     ptx::tc_fence_after();
     issue_st(0);
     ptx::umma_commit(st_ready);
+    PROF_DECL
     for (int s = 0; s < steps; ++s) {
       const int st = s & 1;
       const uint32_t ph = s & 1;
@@ -249,6 +271,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
       const uint32_t da = ptx::smem_u32(do_smem + st * TILE_BYTES);
       // dP^T(s) = V_j dO^T: its columns still hold dQ(s-1) until the drain warps are done
       if (s > 0) ptx::mbar_wait(dq_drained, ph ^ 1, abort_flag, p.status, 44);
+      PROF(0);
       ptx::tc_fence_after();
 #pragma unroll
       for (int ks = 0; ks < D / 16; ++ks) {
@@ -258,7 +281,9 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
       }
       ptx::umma_commit(dpt_ready);
       // dV += P^T dO (reduction over the 128 query rows of the tile)
+      PROF(1);
       ptx::mbar_wait(p1_ready, ph, abort_flag, p.status, 45);
+      PROF(2);
       ptx::tc_fence_after();
 #pragma unroll
       for (int ks = 0; ks < 8; ++ks)
@@ -266,39 +291,45 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
                      ptx::make_smem_desc(da + ks * 2048, BOX_BYTES, 1024), IDESC_DKV, (s | ks) != 0);
       // S^T(s+1): overwrites P^T(s), which the dV products above read first (in-order pipe)
       if (s + 1 < steps) {
+        PROF(3);
         ptx::mbar_wait(&qdo_full[st ^ 1], ((s + 1) >> 1) & 1, abort_flag, p.status, 46);
+        PROF(4);
         ptx::tc_fence_after();
         issue_st(st ^ 1);
         ptx::umma_commit(st_ready);
       }
       // dK += dS^T Q, then dQ = dS K into the dP^T columns
+      PROF(5);
       ptx::mbar_wait(p2_ready, ph, abort_flag, p.status, 47);
+      PROF(6);
       ptx::tc_fence_after();
 #pragma unroll
       for (int ks = 0; ks < 8; ++ks)
         ptx::umma_ts(tmem_base + COL_DK, tmem_base + COL_DPT + ks * 8,
                      ptx::make_smem_desc(qa + ks * 2048, BOX_BYTES, 1024), IDESC_DKV, (s | ks) != 0);
+      ptx::umma_commit(&qdo_empty[st]);  // Q_s and dO_s are dead once dK(s) has run
       if constexpr (DQ_T) {
-        ptx::umma_commit(&qdo_empty[st]);
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks)  // dQ^T = K_j^T dS^T, reduction over the 128 key rows
           ptx::umma_ss(tmem_base + COL_DQ, ptx::make_smem_desc(ka + ks * 2048, BOX_BYTES, 1024),
                        ptx::make_smem_desc(sa + ks * 2048, BOX_BYTES, 1024), IDESC_DQT, ks != 0);
       } else {
-        // (the Q/dO stage is released by the drain warps, which first reuse it as dQ staging)
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks)  // reduction over the 128 key rows of the tile
           ptx::umma_ss(tmem_base + COL_DQ, ptx::make_smem_desc(sa + ks * 2048, BOX_BYTES, 1024),
                        ptx::make_smem_desc(ka + ks * 2048, BOX_BYTES, 1024), IDESC_DQ, ks != 0);
       }
       ptx::umma_commit(dq_ready);
+      PROF(7);
     }
+    PROF_FLUSH(0);
     ptx::umma_commit(all_done);
-  } else if (warp >= 4 && warp < 12) {
+  } else if (warp >= 4 && warp < DRAIN_WARP0) {
     // ---------------------------------------------------------------- P^T / dS^T (lane = key row)
-    // warps 4-7 take the query columns [0, 64) of their rows, warps 8-11 the columns [64, 128)
+    // warps 4-7 take the first 128 / CGROUPS query columns of their rows, warps 8-11 the next, ...
     const int quarter = warp & 3;
-    const int half = (warp - 4) >> 2;
+    const int cgrp = (warp - 4) >> 2;
+    const int c0 = NCH * cgrp;  // first 32-column chunk of this thread
     const int r = quarter * 32 + lane;
     const int kv_g = jt * 128 + r;
     const uint32_t lane_off = static_cast<uint32_t>(quarter * 32) << 16;
@@ -309,19 +340,24 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
     if constexpr (MASKED)
       mask_col = reinterpret_cast<const T*>(p.mask) + (long long)b * p.a.ms[0] + (long long)h * p.a.ms[1] +
                  (long long)kv_g * p.a.ms[3];
+    PROF_DECL
     for (int s = 0; s < steps; ++s) {
       const int it = i_begin + (s + jt) % steps;  // staggered start: CTAs of one head add into different dQ tiles
       const int st = s & 1;
       const float4* nlse4 = reinterpret_cast<const float4*>(nlse_smem + st * 128);
       const float4* ndel4 = reinterpret_cast<const float4*>(ndelta_smem + st * 128);
-      uint32_t pp[32];  // this thread's half row of P^T, packed pairs along the query index
+      uint32_t pp[NCH * 16];  // this thread's part of a P^T row, packed pairs along the query index
+      PROF(0);
       ptx::mbar_wait(&qdo_full[st], (s >> 1) & 1, abort_flag, p.status, 48);  // -lse, -delta of the tile
+      PROF(1);
       ptx::mbar_wait(st_ready, s & 1, abort_flag, p.status, 49);
+      PROF(2);
       ptx::tc_fence_after();
       const bool diag = CAUSAL && (it == jt);
       // ---- stage A: P^T = exp2(S^T * scale*log2e - lse*log2e)
       {
-        uint32_t ra[32], rb[32];
+        uint32_t ra[32];
+        [[maybe_unused]] uint32_t rb[32];
         auto stage_a = [&](const uint32_t (&sv)[32], int c, int lc) {
 #pragma unroll
           for (int g = 0; g < 8; ++g) {
@@ -359,18 +395,24 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
             pp[lc * 16 + g * 2 + 1] = am::cvt_pair<T>(p2, p3);
           }
         };
-        const int c0 = 2 * half;
         ptx::tmem_ld32(st_addr + c0 * 32, ra);
         am::tmem_ld_wait_dep(ra);
-        ptx::tmem_ld32(st_addr + c0 * 32 + 32, rb);
+        PROF(3);
+        if constexpr (NCH == 2) ptx::tmem_ld32(st_addr + c0 * 32 + 32, rb);
         stage_a(ra, c0, 0);
-        am::tmem_ld_wait_dep(rb);
-        stage_a(rb, c0 + 1, 1);
-        // both owners of a key row (this warp and its partner four warps away) must have read
-        // their S^T columns before either overwrites them with packed P^T
-        asm volatile("bar.sync 1, 256;" ::: "memory");
+        if constexpr (NCH == 2) {
+          PROF(4);
+          am::tmem_ld_wait_dep(rb);
+          PROF(0);
+          stage_a(rb, c0 + 1, 1);
+        }
+        // all owners of a key row (this warp and its partners four warps apart) must have read
+        // their S^T columns before any of them overwrites them with packed P^T
+        PROF(4);
+        asm volatile("bar.sync 1, %0;" ::"n"(COMPUTE_WARPS * 32) : "memory");
+        PROF(5);
 #pragma unroll
-        for (int lc = 0; lc < 2; ++lc) {
+        for (int lc = 0; lc < NCH; ++lc) {
           uint32_t chunk[16];
 #pragma unroll
           for (int i = 0; i < 16; ++i) chunk[i] = pp[lc * 16 + i];
@@ -379,12 +421,15 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
         ptx::tmem_st_wait();
         ptx::tc_fence_before();
         ptx::mbar_arrive(p1_ready);
+        PROF(6);
       }
       // ---- stage B: dS^T = P^T (dP^T - delta)
       ptx::mbar_wait(dpt_ready, s & 1, abort_flag, p.status, 50);
+      PROF(7);
       ptx::tc_fence_after();
       {
-        uint32_t ra[32], rb[32];
+        uint32_t ra[32];
+        [[maybe_unused]] uint32_t rb[32];
         auto stage_b = [&](const uint32_t (&dv)[32], int c, int lc) {
           uint32_t dd[16];
 #pragma unroll
@@ -416,16 +461,20 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
                 make_uint4(dd[g * 4 + 0], dd[g * 4 + 1], dd[g * 4 + 2], dd[g * 4 + 3]);
           }
         };
-        const int c0 = 2 * half;
         ptx::tmem_ld32(dp_addr + c0 * 32, ra);
         am::tmem_ld_wait_dep(ra);
-        ptx::tmem_ld32(dp_addr + c0 * 32 + 32, rb);
+        PROF(8);
+        if constexpr (NCH == 2) ptx::tmem_ld32(dp_addr + c0 * 32 + 32, rb);
         stage_b(ra, c0, 0);
-        am::tmem_ld_wait_dep(rb);
-        stage_b(rb, c0 + 1, 1);
-        asm volatile("bar.sync 1, 256;" ::: "memory");  // dP^T fully read before dS^T overwrites it
+        if constexpr (NCH == 2) {
+          am::tmem_ld_wait_dep(rb);
+          stage_b(rb, c0 + 1, 1);
+        }
+        PROF(9);
+        asm volatile("bar.sync 1, %0;" ::"n"(COMPUTE_WARPS * 32) : "memory");  // dP^T fully read before dS^T overwrites it
+        PROF(10);
 #pragma unroll
-        for (int lc = 0; lc < 2; ++lc) {
+        for (int lc = 0; lc < NCH; ++lc) {
           uint32_t chunk[16];
 #pragma unroll
           for (int i = 0; i < 16; ++i) chunk[i] = pp[lc * 16 + i];
@@ -435,17 +484,23 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
         ptx::fence_proxy_async_smem();
         ptx::tc_fence_before();
         ptx::mbar_arrive(p2_ready);
+        PROF(11);
       }
     }
+    if (threadIdx.x == 4 * 32) PROF_FLUSH(1);
     // epilogue: dV and dK rows of this key tile
     ptx::mbar_wait(all_done, 0, abort_flag, p.status, 51);
     ptx::tc_fence_after();
     const long long out_row = (((long long)b * p.a.H + h) * p.a.S + kv_g) * D;
     T* dv_row = reinterpret_cast<T*>(p.dv) + out_row;
     T* dk_row = reinterpret_cast<T*>(p.dk) + out_row;
+    // the first half of the column groups writes dV, the second half dK; a group takes
+    // D * 2 / CGROUPS feature columns of its matrix
+    constexpr int EPI_CHUNKS = D / 32 * 2 / CGROUPS;
 #pragma unroll 1
-    for (int cc = 0; cc < D / 32; ++cc) {
-      const bool is_k = half == 1;  // warps 4-7 write dV, warps 8-11 write dK
+    for (int ci = 0; ci < EPI_CHUNKS; ++ci) {
+      const bool is_k = cgrp >= CGROUPS / 2;
+      const int cc = (cgrp % (CGROUPS / 2)) * EPI_CHUNKS + ci;
       const float mul = is_k ? p.a.scale : 1.f;
       uint32_t rr[32];
       ptx::tmem_ld32(tmem_base + lane_off + (is_k ? COL_DK : COL_DV) + cc * 32, rr);
@@ -461,19 +516,21 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
         *reinterpret_cast<uint4*>(dst + g * 8) = o;
       }
     }
-  } else if (warp >= 12) {
-    // ---------------------------------------------------------------- dQ drain (lane = query row)
+  } else if (warp >= DRAIN_WARP0) {
+    // ---------------------------------------------------------------- dQ drain
     const int quarter = warp & 3;
     const int r = quarter * 32 + lane;
     const uint32_t dq_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + COL_DQ;
     const long long row_base = ((long long)b * p.a.H + h) * p.a.S;
+    PROF_DECL
     for (int s = 0; s < steps; ++s) {
       const int it = i_begin + (s + jt) % steps;  // staggered start: CTAs of one head add into different dQ tiles
-      const int st = s & 1;
+      PROF(0);
       ptx::mbar_wait(dq_ready, s & 1, abort_flag, p.status, 52);
+      PROF(1);
       ptx::tc_fence_after();
       if constexpr (DQ_T) {
-        // this thread owns feature d = r of the tile's 128 query rows
+        // lane = feature d: this thread owns feature d = r of the tile's 128 query rows
         float* dst = p.dq_acc + (row_base + (long long)it * 128) * D + r;
 #pragma unroll
         for (int c = 0; c < 4; c += 2) {
@@ -485,51 +542,50 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
           if (c == 2) {  // tensor memory released as soon as its values sit in registers
             ptx::tc_fence_before();
             ptx::mbar_arrive(dq_drained);
+            PROF(2);
           }
 #pragma unroll
           for (int i = 0; i < 32; ++i) red_add_f32(dst + (long long)(c * 32 + i) * D, __uint_as_float(r0[i]));
 #pragma unroll
           for (int i = 0; i < 32; ++i) red_add_f32(dst + (long long)(c * 32 + 32 + i) * D, __uint_as_float(r1[i]));
         }
-        continue;
-      }
-      // dQ(s) complete implies dK(s) complete (in-order pipe): Q_s and dO_s are dead, and their
-      // shared memory (D/32 boxes of [128 rows][32 floats], 16 KB each) stages dQ_i
-      uint8_t* stage_q = q_smem + st * TILE_BYTES;
-      uint8_t* stage_do = do_smem + st * TILE_BYTES;
-      auto box_ptr = [&](int j) { return (j < D / 64 ? stage_q : stage_do) + (j % (D / 64)) * 16384; };
-#pragma unroll
-      for (int c = 0; c < D / 32; c += 2) {
+        PROF(3);
+      } else {
+        // lane = query row; dQ_i leaves through a staging tile of D/32 boxes of [128 rows][32
+        // floats] (16 KB each) and bulk tensor reduce-add copies
+        static_assert(D == 64, "the staging path is written for two boxes");
         uint32_t r0[32], r1[32];
-        ptx::tmem_ld32(dq_addr + c * 32, r0);
-        ptx::tmem_ld32(dq_addr + c * 32 + 32, r1);
+        ptx::tmem_ld32(dq_addr, r0);
+        ptx::tmem_ld32(dq_addr + 32, r1);
         am::tmem_ld_wait_dep(r0);
         am::tmem_ld_wait_dep(r1);
-        if (c + 2 >= D / 32) {  // tensor memory released as soon as its values sit in registers
-          ptx::tc_fence_before();
-          ptx::mbar_arrive(dq_drained);
-        }
-        uint8_t* row0 = box_ptr(c) + r * 128;
-        uint8_t* row1 = box_ptr(c + 1) + r * 128;
+        ptx::tc_fence_before();
+        ptx::mbar_arrive(dq_drained);  // tensor memory released as soon as its values sit in registers
+        PROF(2);
+        // the copies of the previous tile must have read the staging tile before it is rewritten
+        if (threadIdx.x == DRAIN_WARP0 * 32) bulk_wait_group_read0();
+        asm volatile("bar.sync 2, 128;" ::: "memory");
+        uint8_t* row0 = dq_stage + r * 128;
+        uint8_t* row1 = dq_stage + 16384 + r * 128;
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
           const int chunk = (k ^ (r & 7)) * 16;  // 128-byte swizzle: conflict-free and what the copy expects
           *reinterpret_cast<uint4*>(row0 + chunk) = make_uint4(r0[k * 4], r0[k * 4 + 1], r0[k * 4 + 2], r0[k * 4 + 3]);
           *reinterpret_cast<uint4*>(row1 + chunk) = make_uint4(r1[k * 4], r1[k * 4 + 1], r1[k * 4 + 2], r1[k * 4 + 3]);
         }
-      }
-      ptx::fence_proxy_async_smem();
-      asm volatile("bar.sync 2, 128;" ::: "memory");
-      if (threadIdx.x == 12 * 32) {
-        const int y = (int)(row_base + (long long)it * 128);
-#pragma unroll
-        for (int j = 0; j < D / 32; ++j) tma_reduce_add_2d(&map_dq, box_ptr(j), j * 32, y);
-        bulk_commit_group();
-        bulk_wait_group_read0();          // staging read out: the producer may refill the stage
-        ptx::mbar_arrive(&qdo_empty[st]);
+        ptx::fence_proxy_async_smem();
+        asm volatile("bar.sync 2, 128;" ::: "memory");
+        if (threadIdx.x == DRAIN_WARP0 * 32) {
+          const int y = (int)(row_base + (long long)it * 128);
+          tma_reduce_add_2d(&map_dq, dq_stage, 0, y);
+          tma_reduce_add_2d(&map_dq, dq_stage + 16384, 32, y);
+          bulk_commit_group();
+        }
+        PROF(3);
       }
     }
-    if (threadIdx.x == 12 * 32) bulk_wait_group0();  // every reduce-add has landed before the CTA ends
+    if (threadIdx.x == DRAIN_WARP0 * 32) bulk_wait_group0();  // every reduce-add has landed before the CTA ends
+    if (threadIdx.x == DRAIN_WARP0 * 32) PROF_FLUSH(2);
   }
   ptx::tc_fence_before();
   __syncthreads();
@@ -616,7 +672,8 @@ static bool make_dq_map(CUtensorMap* map, float* base, uint64_t rows, uint64_t D
 template <typename T, int D, bool CAUSAL, bool MASKED>
 static int launch_bwd(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& md,
                       const CUtensorMap& mdq, const CUtensorMap& mmask, const BwdParams& p, cudaStream_t st) {
-  constexpr int SMEM = 6 * 128 * D * 2 + 128 * 128 * 2 + 2048 + 128 + ((MASKED && D == 64) ? 2 * 128 * 128 * 2 : 0);
+  constexpr int SMEM = 6 * 128 * D * 2 + 128 * 128 * 2 + 2048 + 128 + ((MASKED && D == 64) ? 2 * 128 * 128 * 2 : 0) +
+                       (D == 64 ? 128 * D * 4 : 0);
   auto kern = attn_bwd_tc_kernel<T, D, CAUSAL, MASKED>;
   static std::once_flag once;
   static cudaError_t attr_err = cudaSuccess;
@@ -626,7 +683,7 @@ static int launch_bwd(const CUtensorMap& mq, const CUtensorMap& mk, const CUtens
     return (int)attr_err;
   }
   dim3 grid((unsigned)p.nq, (unsigned)(p.a.B * p.a.H));
-  kern<<<grid, BWD_THREADS, SMEM, st>>>(mq, mk, mv, md, mdq, mmask, p);
+  kern<<<grid, bwd_threads_for(D, MASKED), SMEM, st>>>(mq, mk, mv, md, mdq, mmask, p);
   return launch_status("attn_bwd_tc");
 }
 
@@ -700,3 +757,9 @@ int launch_attn_bwd_tc(void* dq, void* dk, void* dv, const void* dout, const voi
 }
 
 }  // namespace tb200
+
+#ifdef TB200_ATTN_PROFILE
+extern "C" int tb200_debug_read_prof(long long* out) {
+  return (int)cudaMemcpyFromSymbol(out, tb200::g_prof, sizeof(long long) * 64);
+}
+#endif

@@ -130,8 +130,17 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int pair = (int)gridDim.x - 1 - (int)blockIdx.x;  // longest (causal) work first
-  const int bh = blockIdx.y;
+  // CTAs are numbered x-fastest. With a mask that is broadcast over heads the head index is
+  // made the fastest one instead, so that the H CTAs that read the same mask tiles run at the
+  // same time and all but one of them find the tiles in L2.
+  int bx = blockIdx.x, bh = blockIdx.y;
+  if (MASKED && p.a.ms[1] == 0 && p.a.H > 1) {
+    const int lin = (int)blockIdx.x + (int)gridDim.x * (int)blockIdx.y;
+    const int rest = lin / (int)p.a.H;
+    bx = rest % (int)gridDim.x;
+    bh = (rest / (int)gridDim.x) * (int)p.a.H + lin % (int)p.a.H;
+  }
+  const int pair = (int)gridDim.x - 1 - bx;  // longest (causal) work first
   const int b = bh / (int)p.a.H, h = bh % (int)p.a.H;
   const int qt0 = 2 * pair, qt1 = 2 * pair + 1;
   const bool active1 = qt1 < p.nq;
