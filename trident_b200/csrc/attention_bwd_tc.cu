@@ -532,23 +532,29 @@ __global__ void __launch_bounds__(bwd_threads_for(D, MASKED), 1)
       if constexpr (DQ_T) {
         // lane = feature d: this thread owns feature d = r of the tile's 128 query rows
         float* dst = p.dq_acc + (row_base + (long long)it * 128) * D + r;
+        // Three of the four 32-column blocks are loaded at once; the fourth reuses the
+        // registers of the first after its reductions are issued, so that only 32 of the
+        // 128 reductions stand between the product and the release of the tensor memory.
+        uint32_t r0[32], r1[32], r2[32];
+        ptx::tmem_ld32(dq_addr, r0);
+        ptx::tmem_ld32(dq_addr + 32, r1);
+        ptx::tmem_ld32(dq_addr + 64, r2);
+        am::tmem_ld_wait_dep(r0);
+        am::tmem_ld_wait_dep(r1);
+        am::tmem_ld_wait_dep(r2);
 #pragma unroll
-        for (int c = 0; c < 4; c += 2) {
-          uint32_t r0[32], r1[32];
-          ptx::tmem_ld32(dq_addr + c * 32, r0);
-          ptx::tmem_ld32(dq_addr + c * 32 + 32, r1);
-          am::tmem_ld_wait_dep(r0);
-          am::tmem_ld_wait_dep(r1);
-          if (c == 2) {  // tensor memory released as soon as its values sit in registers
-            ptx::tc_fence_before();
-            ptx::mbar_arrive(dq_drained);
-            PROF(2);
-          }
+        for (int i = 0; i < 32; ++i) red_add_f32(dst + (long long)i * D, __uint_as_float(r0[i]));
+        ptx::tmem_ld32(dq_addr + 96, r0);
+        am::tmem_ld_wait_dep(r0);
+        ptx::tc_fence_before();
+        ptx::mbar_arrive(dq_drained);  // tensor memory released as soon as its values sit in registers
+        PROF(2);
 #pragma unroll
-          for (int i = 0; i < 32; ++i) red_add_f32(dst + (long long)(c * 32 + i) * D, __uint_as_float(r0[i]));
+        for (int i = 0; i < 32; ++i) red_add_f32(dst + (long long)(32 + i) * D, __uint_as_float(r1[i]));
 #pragma unroll
-          for (int i = 0; i < 32; ++i) red_add_f32(dst + (long long)(c * 32 + 32 + i) * D, __uint_as_float(r1[i]));
-        }
+        for (int i = 0; i < 32; ++i) red_add_f32(dst + (long long)(64 + i) * D, __uint_as_float(r2[i]));
+#pragma unroll
+        for (int i = 0; i < 32; ++i) red_add_f32(dst + (long long)(96 + i) * D, __uint_as_float(r0[i]));
         PROF(3);
       } else {
         // lane = query row; dQ_i leaves through a staging tile of D/32 boxes of [128 rows][32

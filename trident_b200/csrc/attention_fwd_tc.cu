@@ -99,6 +99,17 @@ __device__ inline void load_mask32(float (&mv)[32], const T* row, long long col,
   }
 }
 
+#ifdef TB200_ATTN_PROFILE
+__device__ long long g_prof_fwd[64];
+#define PROF_DECL long long prof_acc[12] = {0}; long long prof_last = clock64(); const bool prof_on = blockIdx.x == 0 && blockIdx.y == 0;
+#define PROF(slot) do { if (prof_on) { long long t_ = clock64(); prof_acc[slot] += t_ - prof_last; prof_last = t_; } } while (0)
+#define PROF_FLUSH(role) do { if (prof_on) for (int i_ = 0; i_ < 12; ++i_) g_prof_fwd[(role) * 16 + i_] = prof_acc[i_]; } while (0)
+#else
+#define PROF_DECL
+#define PROF(slot)
+#define PROF_FLUSH(role)
+#endif
+
 template <typename T, int D, bool CAUSAL, bool MASKED>
 __global__ void __launch_bounds__(FWD_THREADS, 1)
     attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
@@ -170,6 +181,16 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
   ptx::tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
+  // Register allowance: the four service warps give registers back and the eight softmax warps
+  // (two warpgroups) take them. An increase waits, without a bound, until the CTA's own pool
+  // (the registers it was launched with) holds enough, so the totals are checked at compile
+  // time: a sum above the launch allocation would block the softmax warps for ever.
+  constexpr int REGS_LAUNCH = 168, REGS_SERVICE = 48, REGS_SOFTMAX = 224;
+  static_assert(FWD_THREADS == 384 && REGS_LAUNCH * FWD_THREADS <= 65536, "launch allocation");
+  static_assert(4 * 32 * REGS_SERVICE + 8 * 32 * REGS_SOFTMAX <= REGS_LAUNCH * FWD_THREADS,
+                "register pool of the CTA exceeded: setmaxnreg.inc would never return");
+  if (warp < 4) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(REGS_SERVICE));
   if (warp == 0 && lane == 0) {
     // ---------------------------------------------------------------- producer
     ptx::mbar_expect_tx(&q_full[0], TILE_BYTES);
@@ -227,21 +248,27 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
       ptx::umma_commit(&s_full[1]);
     }
     ptx::umma_commit(&k_empty[0]);
+    PROF_DECL
     for (int j = 0; j < nmax; ++j) {
       const int st = j & 1, nst = (j + 1) & 1;
       const uint32_t ph = (j >> 1) & 1, nph = ((j + 1) >> 1) & 1;
       const uint32_t jp = j & 1;
       bool k_next_ready = false;
       if (j < n0) {
+        PROF(0);
         ptx::mbar_wait(&p_full[0], jp, abort_flag, p.status, 24);
+        PROF(1);
         ptx::mbar_wait(&v_full[st], ph, abort_flag, p.status, 25);
+        PROF(2);
         ptx::tc_fence_after();
         issue_pv(0, st, j > 0);
         ptx::umma_commit(&o_done[0]);
         if (j >= n1) ptx::umma_commit(&v_empty[st]);
       }
       if (j + 1 < n0) {
+        PROF(3);
         ptx::mbar_wait(&k_full[nst], nph, abort_flag, p.status, 26);
+        PROF(4);
         k_next_ready = true;
         ptx::tc_fence_after();
         issue_qk(0, nst);
@@ -249,7 +276,9 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
         if (j + 1 >= n1) ptx::umma_commit(&k_empty[nst]);
       }
       if (j < n1) {
+        PROF(5);
         ptx::mbar_wait(&p_full[1], jp, abort_flag, p.status, 27);
+        PROF(6);
         ptx::mbar_wait(&v_full[st], ph, abort_flag, p.status, 28);
         ptx::tc_fence_after();
         issue_pv(1, st, j > 0);
@@ -263,9 +292,13 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
         ptx::umma_commit(&s_full[1]);
         ptx::umma_commit(&k_empty[nst]);
       }
+      PROF(7);
     }
-  } else if (warp >= 4) {
+    PROF_FLUSH(0);
+  }
+  } else {
     // ---------------------------------------------------------------- softmax + epilogue
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(REGS_SOFTMAX));
     const int t = (warp - 4) >> 2;
     const int quarter = warp & 3;
     const int n = t == 0 ? n0 : n1;
@@ -280,6 +313,7 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
       mask_row = reinterpret_cast<const T*>(p.mask) + (long long)b * p.a.ms[0] + (long long)h * p.a.ms[1] +
                  row_g * p.a.ms[2];
     float m_used = -INFINITY, l = 0.f;
+    PROF_DECL
     for (int j = 0; j < n; ++j) {
       const long long kv0 = (long long)j * TK;
       // the 128 mask values of this row and key tile are fetched before the scores are waited
@@ -304,16 +338,21 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
           load_mask32<T>(mv, mask_row, kv0 + c * 32, p.a.ms[3], false);
         }
       };
+      PROF(0);
       ptx::mbar_wait(&s_full[t], j & 1, abort_flag, p.status, 31);
+      PROF(1);
       ptx::tc_fence_after();
       const bool diag = CAUSAL && (j == n - 1);
+      // The row's 128 scores are read from tensor memory once and stay in registers between
+      // the maximum and the exponentials (the softmax warps raise their register allowance
+      // for that): raw accumulator bits on the plain path, scaled and masked values otherwise.
+      uint32_t sr[4][32];
       // pass 1: row maximum of the scaled (and masked) scores, in log2 units
       float mx = -INFINITY;
       const bool plain = !MASKED && !diag;  // uniform over the CTA's softmax warps of this tile
       if (plain) {
         // raw maximum (the scale is positive), two elements per three-input max, the load of
         // the next 32 columns in flight while the current ones are reduced
-        uint32_t ra[32], rb[32];
         float m0 = -INFINITY, m1 = -INFINITY;
         auto reduce32 = [&](const uint32_t (&r)[32]) {
 #pragma unroll
@@ -322,37 +361,47 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
             m1 = am::max3(m1, __uint_as_float(r[i + 2]), __uint_as_float(r[i + 3]));
           }
         };
-        ptx::tmem_ld32(s_addr, ra);
-        am::tmem_ld_wait_dep(ra);
-        ptx::tmem_ld32(s_addr + 32, rb);
-        reduce32(ra);
-        am::tmem_ld_wait_dep(rb);
-        ptx::tmem_ld32(s_addr + 64, ra);
-        reduce32(rb);
-        am::tmem_ld_wait_dep(ra);
-        ptx::tmem_ld32(s_addr + 96, rb);
-        reduce32(ra);
-        am::tmem_ld_wait_dep(rb);
-        reduce32(rb);
+        ptx::tmem_ld32(s_addr, sr[0]);
+        am::tmem_ld_wait_dep(sr[0]);
+        ptx::tmem_ld32(s_addr + 32, sr[1]);
+        reduce32(sr[0]);
+        am::tmem_ld_wait_dep(sr[1]);
+        ptx::tmem_ld32(s_addr + 64, sr[2]);
+        reduce32(sr[1]);
+        am::tmem_ld_wait_dep(sr[2]);
+        ptx::tmem_ld32(s_addr + 96, sr[3]);
+        reduce32(sr[2]);
+        am::tmem_ld_wait_dep(sr[3]);
+        reduce32(sr[3]);
         mx = fmaxf(m0, m1) * p.scale_log2;
       } else {
         const int lim = CAUSAL ? row_in_tile : 1 << 30;  // columns above `lim` are masked (diagonal tile)
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          uint32_t r[32];
-          ptx::tmem_ld32(s_addr + c * 32, r);
-          ptx::tmem_ld_wait();
+        auto scale32 = [&](uint32_t (&r)[32], int c) {
           float mv[32];
           if constexpr (MASKED) mask32(mv, c);
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
-            float s = __uint_as_float(r[i]) * p.scale_log2;
-            if constexpr (MASKED) s += mv[i];
-            if (c * 32 + i > lim) s = -INFINITY;
-            mx = fmaxf(mx, s);
+            float sc = __uint_as_float(r[i]) * p.scale_log2;
+            if constexpr (MASKED) sc += mv[i];
+            if (c * 32 + i > lim) sc = -INFINITY;
+            mx = fmaxf(mx, sc);
+            r[i] = __float_as_uint(sc);
           }
-        }
+        };
+        ptx::tmem_ld32(s_addr, sr[0]);
+        am::tmem_ld_wait_dep(sr[0]);
+        ptx::tmem_ld32(s_addr + 32, sr[1]);
+        scale32(sr[0], 0);
+        am::tmem_ld_wait_dep(sr[1]);
+        ptx::tmem_ld32(s_addr + 64, sr[2]);
+        scale32(sr[1], 1);
+        am::tmem_ld_wait_dep(sr[2]);
+        ptx::tmem_ld32(s_addr + 96, sr[3]);
+        scale32(sr[2], 2);
+        am::tmem_ld_wait_dep(sr[3]);
+        scale32(sr[3], 3);
       }
+      PROF(2);
       const float m_new = fmaxf(m_used, mx);
       if (j == 0) {
         m_used = m_new;
@@ -378,12 +427,12 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
         }
       }
       const float m_safe = m_used == -INFINITY ? 0.f : m_used;
+      PROF(3);
       // pass 2: probabilities, row sum, P written over S as packed 16-bit pairs
-      if (plain) {
-        const uint64_t scale2 = am::pack2f(p.scale_log2, p.scale_log2);
+      {
+        const uint64_t scale2 = plain ? am::pack2f(p.scale_log2, p.scale_log2) : am::pack2f(1.f, 1.f);
         const uint64_t negm2 = am::pack2f(-m_safe, -m_safe);
         uint64_t lsum = am::pack2f(0.f, 0.f);
-        uint32_t ra[32], rb[32];
         auto exp32 = [&](const uint32_t (&r)[32], int c) {
           uint32_t packed[16];
 #pragma unroll
@@ -403,52 +452,22 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
           }
           ptx::tmem_st16(s_addr + c * 16, packed);
         };
-        ptx::tmem_ld32(s_addr, ra);
-        am::tmem_ld_wait_dep(ra);
-        ptx::tmem_ld32(s_addr + 32, rb);
-        exp32(ra, 0);
-        am::tmem_ld_wait_dep(rb);
-        ptx::tmem_ld32(s_addr + 64, ra);
-        exp32(rb, 1);
-        am::tmem_ld_wait_dep(ra);
-        ptx::tmem_ld32(s_addr + 96, rb);
-        exp32(ra, 2);
-        am::tmem_ld_wait_dep(rb);
-        exp32(rb, 3);
+        exp32(sr[0], 0);
+        exp32(sr[1], 1);
+        exp32(sr[2], 2);
+        exp32(sr[3], 3);
         float l0, l1;
         am::unpack2f(lsum, l0, l1);
         l += l0 + l1;
-      } else {
-        const int lim = CAUSAL ? row_in_tile : 1 << 30;
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          uint32_t r[32];
-          ptx::tmem_ld32(s_addr + c * 32, r);
-          ptx::tmem_ld_wait();
-          float mv[32];
-          if constexpr (MASKED) mask32(mv, c);
-          uint32_t packed[16];
-#pragma unroll
-          for (int i = 0; i < 32; i += 2) {
-            float s0 = fmaf(__uint_as_float(r[i]), p.scale_log2, -m_safe);
-            float s1 = fmaf(__uint_as_float(r[i + 1]), p.scale_log2, -m_safe);
-            if constexpr (MASKED) {
-              s0 += mv[i];
-              s1 += mv[i + 1];
-            }
-            if (c * 32 + i > lim) s0 = -INFINITY;
-            if (c * 32 + i + 1 > lim) s1 = -INFINITY;
-            const float p0 = am::ex2(s0), p1 = am::ex2(s1);
-            l += p0 + p1;
-            packed[i >> 1] = am::cvt_pair<T>(p0, p1);
-          }
-          ptx::tmem_st16(s_addr + c * 16, packed);
-        }
       }
+      PROF(4);
       ptx::tmem_st_wait();
       ptx::tc_fence_before();
       ptx::mbar_arrive(&p_full[t]);
+      PROF(5);
     }
+    if (threadIdx.x == 128) PROF_FLUSH(1);
+    if (threadIdx.x == 256) PROF_FLUSH(2);
     if (n > 0) {
       ptx::mbar_wait(&o_done[t], (n - 1) & 1, abort_flag, p.status, 33);
       ptx::tc_fence_after();
@@ -598,3 +617,9 @@ int launch_attn_fwd_tc(void* out, float* lse, const void* q, const void* k, cons
 }
 
 }  // namespace tb200
+
+#ifdef TB200_ATTN_PROFILE
+extern "C" int tb200_debug_read_prof_fwd(long long* out) {
+  return (int)cudaMemcpyFromSymbol(out, tb200::g_prof_fwd, sizeof(long long) * 64);
+}
+#endif
