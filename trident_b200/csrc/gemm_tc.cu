@@ -95,6 +95,22 @@ __device__ inline void store_row32(T* dst, const float* v, int valid) {
   }
 }
 
+// Order of the output tiles. The CTAs of the persistent grid work on consecutive tile numbers at
+// the same time, so a "wave" of them should touch as few distinct A row blocks and B column
+// blocks as possible: tiles are numbered m-fastest inside groups of RASTER_GROUP row blocks, which
+// makes a wave of 148 tiles cover about 16 row blocks x 9 column blocks (instead of 148 x 1, which
+// re-read the whole A operand from HBM once per column block).
+constexpr int RASTER_GROUP = 16;
+__device__ inline void tile_coords(int tile, int num_m, int num_n, int& m_tile, int& n_tile) {
+  const int per_group = RASTER_GROUP * num_n;
+  const int group = tile / per_group;
+  const int first_m = group * RASTER_GROUP;
+  const int rows = min(RASTER_GROUP, num_m - first_m);
+  const int in_group = tile - group * per_group;
+  m_tile = first_m + in_group % rows;
+  n_tile = in_group / rows;
+}
+
 template <typename T, bool A_KMAJOR, bool B_KMAJOR, bool GEGLU>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
     gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
@@ -140,8 +156,9 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
     int stage = 0;
     uint32_t phase = 0;
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
-      const int m0 = (tile % p.num_m_tiles) * BM;
-      const int n_tile = tile / p.num_m_tiles;
+      int m_tile, n_tile;
+      tile_coords(tile, p.num_m_tiles, p.num_n_tiles, m_tile, n_tile);
+      const int m0 = m_tile * BM;
       const int n0 = GEGLU ? n_tile * (BN / 2) : n_tile * BN;
       for (int kb = 0; kb < p.num_k_blocks; ++kb) {
         ptx::mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.status, 1);
@@ -215,8 +232,9 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
     T* C = reinterpret_cast<T*>(p.c);
     const T* bias = reinterpret_cast<const T*>(p.bias);
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
-      const int m0 = (tile % p.num_m_tiles) * BM;
-      const int n_tile = tile / p.num_m_tiles;
+      int m_tile, n_tile;
+      tile_coords(tile, p.num_m_tiles, p.num_n_tiles, m_tile, n_tile);
+      const int m0 = m_tile * BM;
       ptx::mbar_wait(&acc_full[acc], acc_phase, abort_flag, p.status, 4);
       ptx::tc_fence_after();
       const int row = m0 + quarter * 32 + lane;
