@@ -160,6 +160,14 @@ int tb200_geglu_fwd(void* out, void* state_gate, const void* x, const void* w,
  * launched at trident/operation/geglu.py:101). */
 int tb200_geglu_bwd_elementwise(void* d_state_gate, const void* dout, const void* state_gate,
                                 int64_t rows, int64_t N, int gelu_tanh, int dtype, void* stream);
+/* The same step fused with the bias gradient of the Linear backward that follows it
+ * (dbias[N] = column sums of d_state_gate, summed in fp32 before rounding): replaces
+ * kernel.GEGLU.backward plus kernel.Linear.backward_bias (trident/kernel/linear.py, launched at
+ * trident/operation/geglu.py:150-178) in one pass over d_state_gate. `workspace` as for
+ * tb200_linear_bwd_bias (tb200_linear_bwd_bias_workspace(rows, N) bytes). */
+int tb200_geglu_bwd_elementwise_bias(void* d_state_gate, void* dbias, const void* dout,
+                                     const void* state_gate, void* workspace, size_t workspace_bytes,
+                                     int64_t rows, int64_t N, int gelu_tanh, int dtype, void* stream);
 
 /* ---- Attention -----------------------------------------------------------
  * out = softmax(scale * q k^T + M) v per (batch, head); M is the additive `mask`

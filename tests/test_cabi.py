@@ -56,6 +56,7 @@ def test_header_cites_reference_for_every_kernel_entry():
         lambda l: l.tb200_linear_fwd(None, None, None, None, 1, 1, 1, 1, 1, 1, 1, 1, 1, 0, 0, None),
         lambda l: l.tb200_geglu_fwd(8, 8, 8, 8, None, 1, 4, 7, 4, 16, 4, 1, 4, 1, 0, 0, 0, None),
         lambda l: l.tb200_geglu_bwd_elementwise(8, 8, 8, 4, 7, 0, 0, None),
+        lambda l: l.tb200_geglu_bwd_elementwise_bias(8, 8, 8, 8, 8, 0, 4, 8, 0, 0, None),
         lambda l: l.tb200_attention_fwd(None, None, None, None, None, None, 1, 1, 8, 16, None, None, None, None, None, 0, 1.0, 0, None),
     ],
 )

@@ -48,6 +48,7 @@ SIGNATURES = {
     "tb200_linear_bwd_bias": (c_int, [c_ptr] * 3 + [c_size, c_i64, c_i64, c_int, c_ptr]),
     "tb200_geglu_fwd": (c_int, [c_ptr] * 5 + [c_i64] * 9 + [c_int, c_int, c_int, c_ptr]),
     "tb200_geglu_bwd_elementwise": (c_int, [c_ptr] * 3 + [c_i64, c_i64, c_int, c_int, c_ptr]),
+    "tb200_geglu_bwd_elementwise_bias": (c_int, [c_ptr] * 5 + [c_size, c_i64, c_i64, c_int, c_int, c_ptr]),
     "tb200_attention_fwd": (
         c_int,
         [c_ptr] * 6 + [c_i64] * 4 + [c_ptr] * 5 + [c_int, c_f32, c_int, c_ptr],
@@ -321,6 +322,19 @@ def geglu_bwd_elementwise(d_state_gate, dout, state_gate, rows, N, gelu_tanh):
             int(bool(gelu_tanh)), dtype_code(dout.dtype), _stream(dout),
         ),
         "tb200_geglu_bwd_elementwise",
+    )
+
+
+def geglu_bwd_elementwise_bias(d_state_gate, dbias, dout, state_gate, workspace, rows, N, gelu_tanh):
+    """d_state_gate as geglu_bwd_elementwise, and dbias[N] = its column sums, in one pass."""
+    _require_cuda(d_state_gate, dbias, dout, state_gate, workspace)
+    _check(
+        load().tb200_geglu_bwd_elementwise_bias(
+            _ptr(d_state_gate), _ptr(dbias), _ptr(dout), _ptr(state_gate), _ptr(workspace),
+            workspace.numel() * workspace.element_size(), rows, N,
+            int(bool(gelu_tanh)), dtype_code(dout.dtype), _stream(dout),
+        ),
+        "tb200_geglu_bwd_elementwise_bias",
     )
 
 

@@ -199,6 +199,71 @@ __global__ void geglu_bwd_elementwise_kernel(T* __restrict__ dsg, const T* __res
   }
 }
 
+// GEGLU backward elementwise step fused with the bias gradient: a CTA owns 32 * V adjacent
+// columns of the state half (and the same columns of the gate half) and a slab of rows; every
+// thread keeps fp32 column sums of what it writes, and the CTA leaves one partial row
+// [2X] per slab for colsum_finalize_kernel. GELU and its derivative share one erf.
+template <typename T, int V>
+__global__ void __launch_bounds__(256)
+    geglu_bwd_bias_kernel(T* __restrict__ dsg, float* __restrict__ partial, const T* __restrict__ dout,
+                          const T* __restrict__ sg, int64_t rows, int64_t X, int64_t rows_per_slab,
+                          int tanh_form) {
+  __shared__ float red[8][2][32 * V + 1];
+  const int64_t j = ((int64_t)blockIdx.x * 32 + threadIdx.x) * V;
+  const int64_t r0 = (int64_t)blockIdx.y * rows_per_slab;
+  const int64_t r1 = min(rows, r0 + rows_per_slab);
+  float acc_s[V], acc_g[V];
+#pragma unroll
+  for (int i = 0; i < V; ++i) acc_s[i] = acc_g[i] = 0.f;
+  if (j < X) {
+    for (int64_t r = r0 + threadIdx.y; r < r1; r += 8) {
+      const T* s = sg + r * 2 * X + j;
+      float sv[V], gv[V], dv[V], ds[V], dg[V];
+      unpack<T>(ld_stream(s), sv);
+      unpack<T>(ld_stream(s + X), gv);
+      unpack<T>(ld_stream(dout + r * X + j), dv);
+#pragma unroll
+      for (int i = 0; i < V; ++i) {
+        const float g = gv[i];
+        float gel, grad;
+        if (tanh_form) {
+          const float a = tanhf(0.7978845608028654f * g * (1.f + 0.044715f * g * g));
+          gel = 0.5f * g * (1.f + a);
+          grad = 0.5f * (1.f + a + g * (1.f - a * a) * (0.7978845608028654f + 0.1070322244089f * g * g));
+        } else {
+          const float cdf = fmaf(0.5f, erff(g * 0.7071067811865476f), 0.5f);
+          gel = g * cdf;
+          grad = fmaf(g * 0.3989422804014327f, __expf(-0.5f * g * g), cdf);
+        }
+        ds[i] = dv[i] * gel;
+        dg[i] = dv[i] * sv[i] * grad;
+        acc_s[i] += ds[i];
+        acc_g[i] += dg[i];
+      }
+      T* d = dsg + r * 2 * X + j;
+      st_stream(d, pack<T>(ds));
+      st_stream(d + X, pack<T>(dg));
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < V; ++i) {
+    red[threadIdx.y][0][threadIdx.x * V + i] = acc_s[i];
+    red[threadIdx.y][1][threadIdx.x * V + i] = acc_g[i];
+  }
+  __syncthreads();
+  const int t = threadIdx.y * 32 + threadIdx.x;
+  for (int c = t; c < 2 * 32 * V; c += 256) {
+    const int which = c / (32 * V), cc = c % (32 * V);
+    const int64_t gc = (int64_t)blockIdx.x * 32 * V + cc;
+    if (gc < X) {
+      float sum = 0.f;
+#pragma unroll
+      for (int y = 0; y < 8; ++y) sum += red[y][which][cc];
+      partial[(int64_t)blockIdx.y * 2 * X + (int64_t)which * X + gc] = sum;
+    }
+  }
+}
+
 int launch_geglu_fwd_elementwise(void* out, const void* sg, int64_t rows, int64_t X, int tanh_form,
                                  int dtype, cudaStream_t st) {
   if (rows == 0 || X == 0) return 0;
@@ -338,6 +403,46 @@ extern "C" int tb200_geglu_bwd_elementwise(void* d_state_gate, const void* dout,
           (T*)d_state_gate, (const T*)dout, (const T*)state_gate, rows, X, gelu_tanh);
     int rc = launch_status("geglu_bwd_elementwise");
     if (rc == 0) note_kernel("elementwise", 1);
+    return rc;
+  });
+}
+
+
+extern "C" int tb200_geglu_bwd_elementwise_bias(void* d_state_gate, void* dbias, const void* dout,
+                                                const void* state_gate, void* workspace,
+                                                size_t workspace_bytes, int64_t rows, int64_t N,
+                                                int gelu_tanh, int dtype, void* stream) {
+  TB200_REQUIRE(d_state_gate && dbias && dout && state_gate && workspace, TB200_ERR_INVALID,
+                "geglu_bwd_elementwise_bias: null pointer");
+  TB200_REQUIRE(rows >= 0 && N > 0 && N % 2 == 0, TB200_ERR_INVALID,
+                "geglu_bwd_elementwise_bias: N must be even and positive");
+  cudaStream_t st = (cudaStream_t)stream;
+  const int64_t X = N / 2;
+  const int64_t slabs = bias_slabs(rows, N);
+  TB200_REQUIRE(workspace_bytes >= (size_t)slabs * N * sizeof(float), TB200_ERR_WORKSPACE,
+                "geglu_bwd_elementwise_bias: workspace too small");
+  const int64_t rows_per_slab = std::max<int64_t>(1, ceil_div(rows, slabs));
+  return dispatch_dtype(dtype, [&](auto tag) -> int {
+    using T = decltype(tag);
+    constexpr int V = Traits<T>::VEC;
+    const bool vec = X % V == 0 && aligned16(d_state_gate) && aligned16(dout) && aligned16(state_gate) &&
+                     aligned16(workspace) && rows > 0;
+    if (!vec) {
+      // widths the vector kernel does not take: the two separate steps
+      int rc = tb200_geglu_bwd_elementwise(d_state_gate, dout, state_gate, rows, N, gelu_tanh, dtype, stream);
+      if (rc) return rc;
+      return tb200_linear_bwd_bias(dbias, d_state_gate, workspace, workspace_bytes, rows, N, dtype, stream);
+    }
+    dim3 block(32, 8), grid((unsigned)ceil_div(X, 32 * V), (unsigned)slabs);
+    geglu_bwd_bias_kernel<T, V><<<grid, block, 0, st>>>((T*)d_state_gate, (float*)workspace, (const T*)dout,
+                                                        (const T*)state_gate, rows, X, rows_per_slab, gelu_tanh);
+    int rc = launch_status("geglu_bwd_bias");
+    if (rc) return rc;
+    dim3 fgrid((unsigned)ceil_div(N, 32), 1), fblock(32, 32);
+    colsum_finalize_kernel<T><<<fgrid, fblock, 0, st>>>((T*)dbias, nullptr, (const float*)workspace, (int)slabs,
+                                                        (int)N);
+    rc = launch_status("colsum_finalize");
+    if (rc == 0) note_kernel("elementwise", 2);
     return rc;
   });
 }

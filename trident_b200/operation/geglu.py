@@ -5,7 +5,6 @@ from typing import Any
 import torch
 
 from trident_b200 import _lib, config, util
-from trident_b200.operation.linear import bias_gradient
 
 
 class GEGLU(torch.autograd.Function):
@@ -73,11 +72,23 @@ class GEGLU(torch.autograd.Function):
         grad_input = torch.empty_like(input)
         grad_weight = torch.empty(weight.shape, device=weight.device, dtype=weight.dtype)
 
-        util.push_trace("tb200_geglu_bwd_elementwise")
-        _lib.geglu_bwd_elementwise(
-            grad_state_gate, grad_output, state_gate, num_batches * m_size, n_size, gelu_tanh
-        )
-        util.pop_trace()
+        rows = num_batches * m_size
+        grad_bias = None
+        if bias is not None:
+            # the bias gradient (column sums of d_state_gate) is taken in the same pass
+            util.push_trace("tb200_geglu_bwd_elementwise_bias")
+            grad_bias = torch.empty(n_size, device=state_gate.device, dtype=state_gate.dtype)
+            workspace = torch.empty(
+                max(_lib.linear_bwd_bias_workspace(rows, n_size), 16), dtype=torch.uint8, device=state_gate.device
+            )
+            _lib.geglu_bwd_elementwise_bias(
+                grad_state_gate, grad_bias, grad_output, state_gate, workspace, rows, n_size, gelu_tanh
+            )
+            util.pop_trace()
+        else:
+            util.push_trace("tb200_geglu_bwd_elementwise")
+            _lib.geglu_bwd_elementwise(grad_state_gate, grad_output, state_gate, rows, n_size, gelu_tanh)
+            util.pop_trace()
 
         util.push_trace("tb200_linear_bwd_input")
         _lib.linear_bwd_input(grad_input, grad_state_gate, weight, use_accelerator)
@@ -86,12 +97,5 @@ class GEGLU(torch.autograd.Function):
         util.push_trace("tb200_linear_bwd_weight")
         _lib.linear_bwd_weight(grad_weight, grad_state_gate, input, use_accelerator)
         util.pop_trace()
-
-        if bias is not None:
-            util.push_trace("tb200_linear_bwd_bias")
-            grad_bias = bias_gradient(grad_state_gate)
-            util.pop_trace()
-        else:
-            grad_bias = None
 
         return grad_input, grad_weight, grad_bias
