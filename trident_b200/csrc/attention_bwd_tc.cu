@@ -601,28 +601,33 @@ __global__ void __launch_bounds__(bwd_threads_for(D, MASKED), 1)
   }
 }
 
-// One warp per (b, h, s) row: ndelta = -sum_d out*dout (out strided, dout contiguous) and
-// nlse2 = -lse * log2(e).
-template <typename T>
-__global__ void attn_bwd_prep_kernel(float* __restrict__ ndelta, float* __restrict__ nlse2,
-                                     const T* __restrict__ out, const T* __restrict__ dout,
-                                     const float* __restrict__ lse, AttnArgs a) {
-  const int lane = threadIdx.x & 31;
-  const int64_t r = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+// ndelta = -sum_d out*dout (out strided over b, h, s; dout contiguous) and nlse2 = -lse * log2(e).
+// D / 8 threads share a (b, h, s) row, each with one 16-byte load of out and of dout, so a warp
+// covers 256 / D rows and moves 1 KB per pair of load instructions.
+template <typename T, int D>
+__global__ void __launch_bounds__(256)
+    attn_bwd_prep_kernel(float* __restrict__ ndelta, float* __restrict__ nlse2, const T* __restrict__ out,
+                         const T* __restrict__ dout, const float* __restrict__ lse, AttnArgs a) {
+  constexpr int TPR = D / 8;           // threads per row
+  constexpr int ROWS_PER_CTA = 256 / TPR;
+  const int sub = threadIdx.x % TPR;
+  const int64_t r = (int64_t)blockIdx.x * ROWS_PER_CTA + threadIdx.x / TPR;
   const int64_t total = a.B * a.H * a.S;
-  if (r >= total) return;
-  const int64_t s = r % a.S, h = (r / a.S) % a.H, b = r / (a.S * a.H);
-  const T* orow = out + b * a.os[0] + h * a.os[1] + s * a.os[2];
-  const T* drow = dout + r * a.D;
+  const bool live = r < total;
   float acc = 0.f;
-  for (int d = lane * 2; d < a.D; d += 64) {
-    float o0, o1, g0, g1;
-    unpack_pair<T>(*reinterpret_cast<const uint32_t*>(orow + d), o0, o1);
-    unpack_pair<T>(*reinterpret_cast<const uint32_t*>(drow + d), g0, g1);
-    acc += o0 * g0 + o1 * g1;
+  if (live) {
+    const int64_t s = r % a.S, h = (r / a.S) % a.H, b = r / (a.S * a.H);
+    const T* orow = out + b * a.os[0] + h * a.os[1] + s * a.os[2] + sub * 8;
+    const T* drow = dout + r * D + sub * 8;
+    float o[8], g[8];
+    unpack<T>(ld_stream(orow), o);
+    unpack<T>(ld_stream(drow), g);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc = fmaf(o[i], g[i], acc);
   }
-  acc = warp_sum(acc);
-  if (lane == 0) {
+#pragma unroll
+  for (int off = TPR / 2; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+  if (live && sub == 0) {
     ndelta[r] = -acc;
     nlse2[r] = -lse[r] * LOG2E;
   }
@@ -743,8 +748,8 @@ int launch_attn_bwd_tc(void* dq, void* dk, void* dv, const void* dout, const voi
   auto go = [&](auto tag, auto dsel) -> int {
     using T = decltype(tag);
     constexpr int D = decltype(dsel)::value;
-    attn_bwd_prep_kernel<T><<<(unsigned)ceil_div(rows, 8), 256, 0, st>>>(ndelta, nlse2, (const T*)out,
-                                                                        (const T*)dout, lse, a);
+    attn_bwd_prep_kernel<T, D><<<(unsigned)ceil_div(rows, 256 / (D / 8)), 256, 0, st>>>(
+        ndelta, nlse2, (const T*)out, (const T*)dout, lse, a);
     int rc = launch_status("attn_bwd_prep");
     if (rc) return rc;
     if (a.causal)
