@@ -273,17 +273,16 @@ def time_e2e(wl, tensors, steps, warmup, world, device):
 
 # DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) of one full-size launch of each
 # workload's dominant kernel, from the ncu captures summarised under profiles/. A launch captured
-# on a quarter of the (batch, head) slices is scaled by 4: the slices are independent, so the traffic
-# grows in proportion. Bytes still in L2 when the kernel ends are not in these figures. None: not captured.
+# on one of the 8 independent batches is scaled by 8 (the traffic grows in proportion). Bytes still in
+# L2 when the kernel ends are not in these figures.
 NCU_TRAFFIC = {
     "softmax": (368.2e6, "profiles/softmax_bwd_vec_fp16_16384x4096.md"),
     "masked_softmax": (367.5e6, "profiles/masked_softmax_vec_fp16_16384x4096.md"),
-    "layer_norm": (36.1e6, "profiles/norm_kernels_layer_norm_fp32_4096x1024_rms_norm_bf16_8192x4096.md"),
-    "rms_norm": (176.2e6, "profiles/norm_kernels_layer_norm_fp32_4096x1024_rms_norm_bf16_8192x4096.md"),
-    "attention_causal": (4 * 289.9e6, "profiles/attn_tc_kernels_bf16_causal_S4096_D128.md (32 of 128 slices, x4)"),
-    "geglu": (None, "profiles/gemm_tc_kernel_bf16_geglu_2048x4096x22016.md (quarter of the rows: 301.0e6; "
-                    "the weight traffic does not scale with rows)"),
-    "attention_masked": (None, "not captured: the full-size mask alone is 8.6 GB"),
+    "layer_norm": (33.7e6, "profiles/norm_kernels_layer_norm_fp32_4096x1024_rms_norm_bf16_8192x4096.md"),
+    "rms_norm": (168.3e6, "profiles/norm_kernels_layer_norm_fp32_4096x1024_rms_norm_bf16_8192x4096.md"),
+    "attention_causal": (1305.2e6, "profiles/attn_tc_kernels_bf16_causal_S4096_D128.md (full-size capture)"),
+    "geglu": (1364.4e6, "profiles/gemm_tc_kernel_bf16_geglu_2048x4096x22016.md (full-size capture)"),
+    "attention_masked": (8 * 5139.2e6, "profiles/attn_tc_kernels_bf16_masked_S16384_D64.md (one of 8 batches, x8)"),
 }
 
 
