@@ -70,7 +70,7 @@ def _table(title, buf, phases, steps):
             print(f"      {label:44s} {v:8.0f}")
 
 
-def run(B=1, H=8, S=4096, D=128, causal=True):
+def run(B=1, H=8, S=4096, D=128, causal=True, masked=False):
     import torch
 
     from . import _lib
@@ -89,14 +89,21 @@ def run(B=1, H=8, S=4096, D=128, causal=True):
     dq, dk, dv = torch.empty_like(q), torch.empty_like(q), torch.empty_like(q)
     ws = torch.empty(_lib.attention_bwd_workspace(B, H, S, D, q.dtype), dtype=torch.uint8, device="cuda")
     scale = D ** -0.5
+    mask = None
+    if masked:  # additive mask broadcast over heads, 10 % -inf, first key never masked
+        causal = False
+        mask = torch.zeros(B, 1, S, S, device="cuda", dtype=torch.bfloat16)
+        mask.masked_fill_(torch.rand(B, 1, S, S, device="cuda", generator=g) < 0.1, float("-inf"))
+        mask[..., 0] = 0
     for _ in range(3):
-        _lib.attention_fwd(out, lse, q, k, v, None, causal, scale)
-        _lib.attention_bwd(dq, dk, dv, None, dy, q, k, v, out, lse, None, ws, causal, scale)
+        _lib.attention_fwd(out, lse, q, k, v, mask, causal, scale)
+        _lib.attention_bwd(dq, dk, dv, None, dy, q, k, v, out, lse, mask, ws, causal, scale)
     torch.cuda.synchronize()
     buf = (ctypes.c_longlong * 64)()
     tiles = S // 128  # CTA (0, 0) owns the longest row of tiles in both kernels
     lib.tb200_debug_read_prof_fwd(buf)
-    _table(f"forward, q,k,v [{B},{H},{S},{D}] bf16, causal={causal}: CTA (0,0), {tiles} key tiles", buf, FWD_PHASES, tiles)
+    _table(f"forward, q,k,v [{B},{H},{S},{D}] bf16, causal={causal}, masked={masked}: CTA (0,0), {tiles} key tiles",
+           buf, FWD_PHASES, tiles)
     lib.tb200_debug_read_prof(buf)
     _table(f"backward, same inputs: CTA (0,0), {tiles} query tiles", buf, BWD_PHASES, tiles)
     print("device status", _lib.device_status(False))
@@ -107,4 +114,7 @@ if __name__ == "__main__":
     if "--build-only" in sys.argv:
         print(path)
     else:
-        run(causal="--full" not in sys.argv)
+        if "--masked" in sys.argv:  # the long-sequence configuration's head size and mask, shorter sequence
+            run(B=1, H=16, S=4096, D=64, masked=True)
+        else:
+            run(causal="--full" not in sys.argv)
