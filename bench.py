@@ -49,6 +49,7 @@ CPU_SAMPLE = {
     "geglu": ({"scale": 32}, "256 of 8192 rows, full weight"),
     "attention_causal": ({"scale": 16}, "8 of 128 (batch, head) slices"),
     "attention_masked": ({"scale": 16, "_world": 8}, "1 of 128 (batch, head) slices, one mask slab"),
+    "var_mean": ({"scale": 4}, "4096 of 16384 rows"),
 }
 
 
@@ -298,6 +299,14 @@ def dominant_kernel(wl, tensors):
         _lib.softmax_fwd(y, x, None, x.shape[0], x.shape[1], x.stride(0), 1)
         return ("softmax_bwd_vec", lambda: _lib.softmax_bwd(dx, dy, y, x.shape[0], x.shape[1], x.stride(0), 1),
                 3.0 * x.numel() * x.element_size())
+    if wl.name == "var_mean":
+        x, dy = tensors["x"], tensors["dy"]
+        rows, cols = x.shape
+        dx = torch.empty_like(x)
+        gv, gm = dy[:, 0].contiguous(), dy[:, 1].contiguous()
+        return ("reduce_bwd_vec (var_mean)",
+                lambda: _lib.reduce_bwd(dx, gv, gm, x, rows, cols, x.stride(0), 1, "var_mean", 1.0),
+                2.0 * x.numel() * x.element_size())
     if wl.name == "layer_norm":
         x, dy, w = tensors["x"], tensors["dy"], tensors["w"]
         rows, cols = x.shape

@@ -169,6 +169,24 @@ int tb200_geglu_bwd_elementwise_bias(void* d_state_gate, void* dbias, const void
                                      const void* state_gate, void* workspace, size_t workspace_bytes,
                                      int64_t rows, int64_t N, int gelu_tanh, int dtype, void* stream);
 
+/* ---- Row reductions: Sum, Mean, Var, VarMean --------------------------------
+ * The problem as util.size_and_stride describes it (trident/util/util.py:65-76): y_size
+ * outputs, output y reduces the x_size elements x[y*y_stride + i*x_stride]. kind: 0 sum,
+ * 1 mean, 2 var, 3 var_mean. out_a[y_size] = sum | mean | var | var, out_b[y_size] = mean
+ * (var_mean only, else ignored); var divides by (x_size - correction).
+ * Replaces kernel.Sum/Mean/Var/VarMean.forward (trident/kernel/sum.py:35, mean.py:35, var.py:35,
+ * var_mean.py:35; launched at trident/operation/sum.py:57, mean.py:58, var.py:59, var_mean.py:60). */
+int tb200_reduce_fwd(void* out_a, void* out_b /*nullable*/, const void* x, int64_t y_size, int64_t x_size,
+                     int64_t y_stride, int64_t x_stride, int kind, float correction, int dtype,
+                     void* stream);
+/* dx (same strides as x) from dout_a[y_size] (and dout_b, the gradient of the mean output of
+ * var_mean, nullable); x is needed for var and var_mean only. Replaces kernel.*.backward of the
+ * same files (trident/kernel/sum.py:65, mean.py:66, var.py:76, var_mean.py:86; launched at
+ * trident/operation/sum.py:79, mean.py:80, var.py:82, var_mean.py:86); no zero fill of dx is needed. */
+int tb200_reduce_bwd(void* dx, const void* dout_a, const void* dout_b /*nullable*/, const void* x /*nullable for sum, mean*/,
+                     int64_t y_size, int64_t x_size, int64_t y_stride, int64_t x_stride, int kind,
+                     float correction, int dtype, void* stream);
+
 /* ---- Attention -----------------------------------------------------------
  * out = softmax(scale * q k^T + M) v per (batch, head); M is the additive `mask`
  * (nullable; same dtype as q; stride 0 broadcasts a dimension) or the causal mask.

@@ -41,6 +41,26 @@ def masked_softmax(input, mask, dim):
     return torch.nn.functional.softmax(filled, 0 if dim == 0 else -1)
 
 
+def sum(input, dim):
+    """tests/test_sum.py:22-29 compares against torch.sum."""
+    return torch.sum(input, dim)
+
+
+def mean(input, dim):
+    """tests/test_mean.py:22-29 compares against torch.mean."""
+    return torch.mean(input, dim)
+
+
+def var(input, dim, correction=1):
+    """tests/test_var.py:22-26 compares against torch.var."""
+    return torch.var(input, dim, correction=correction)
+
+
+def var_mean(input, dim, correction=1):
+    """tests/test_var_mean.py compares against torch.var_mean."""
+    return torch.var_mean(input, dim, correction=correction)
+
+
 def linear(input, weight, bias=None):
     """tests/test_linear.py:27-36 compares against torch.nn.functional.linear."""
     return torch.nn.functional.linear(input, weight, bias)

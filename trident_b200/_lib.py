@@ -39,6 +39,8 @@ SIGNATURES = {
     "tb200_rms_norm_fwd": (c_int, [c_ptr] * 5 + [c_i64] * 5 + [c_f32, c_int, c_ptr]),
     "tb200_rms_norm_bwd_workspace": (c_size, [c_i64, c_i64]),
     "tb200_rms_norm_bwd": (c_int, [c_ptr] * 8 + [c_size] + [c_i64] * 5 + [c_f32, c_int, c_ptr]),
+    "tb200_reduce_fwd": (c_int, [c_ptr] * 3 + [c_i64] * 4 + [c_int, c_f32, c_int, c_ptr]),
+    "tb200_reduce_bwd": (c_int, [c_ptr] * 4 + [c_i64] * 4 + [c_int, c_f32, c_int, c_ptr]),
     "tb200_softmax_fwd": (c_int, [c_ptr] * 3 + [c_i64] * 6 + [c_int, c_ptr]),
     "tb200_softmax_bwd": (c_int, [c_ptr] * 3 + [c_i64] * 4 + [c_int, c_ptr]),
     "tb200_linear_fwd": (c_int, [c_ptr] * 4 + [c_i64] * 9 + [c_int, c_int, c_ptr]),
@@ -215,6 +217,31 @@ def rms_norm_bwd(dx, dweight, dbias, dy, x, weight, rms, workspace, rows, cols, 
             rows, cols, row_stride, col_stride, partial, eps, dtype_code(x.dtype), _stream(x),
         ),
         "tb200_rms_norm_bwd",
+    )
+
+
+REDUCE_KINDS = {"sum": 0, "mean": 1, "var": 2, "var_mean": 3}
+
+
+def reduce_fwd(out_a, out_b, x, y_size, x_size, y_stride, x_stride, kind, correction=0.0):
+    _require_cuda(out_a, out_b, x)
+    _check(
+        load().tb200_reduce_fwd(
+            _ptr(out_a), _ptr(out_b), _ptr(x), y_size, x_size, y_stride, x_stride,
+            REDUCE_KINDS[kind], float(correction), dtype_code(x.dtype), _stream(x),
+        ),
+        "tb200_reduce_fwd",
+    )
+
+
+def reduce_bwd(dx, dout_a, dout_b, x, y_size, x_size, y_stride, x_stride, kind, correction=0.0):
+    _require_cuda(dx, dout_a, dout_b, x)
+    _check(
+        load().tb200_reduce_bwd(
+            _ptr(dx), _ptr(dout_a), _ptr(dout_b), _ptr(x), y_size, x_size, y_stride, x_stride,
+            REDUCE_KINDS[kind], float(correction), dtype_code(dx.dtype), _stream(dx),
+        ),
+        "tb200_reduce_bwd",
     )
 
 

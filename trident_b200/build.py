@@ -17,6 +17,7 @@ SOURCES = [
     "api.cu",
     "row_norm.cu",
     "softmax.cu",
+    "reduce.cu",
     "gemm_simt.cu",
     "gemm_tc.cu",
     "attention_simt.cu",

@@ -3,7 +3,10 @@ from .geglu import GEGLU
 from .layer_norm import LayerNorm
 from .linear import Linear
 from .masked_softmax import MaskedSoftmax
+from .reduce import Mean, Sum, Var, VarMean
 from .rms_norm import RMSNorm
 from .softmax import Softmax
 
-__all__ = ["Attention", "GEGLU", "LayerNorm", "Linear", "MaskedSoftmax", "RMSNorm", "Softmax"]
+__all__ = [
+    "Attention", "GEGLU", "LayerNorm", "Linear", "MaskedSoftmax", "Mean", "RMSNorm", "Softmax", "Sum", "Var", "VarMean",
+]

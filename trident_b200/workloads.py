@@ -128,6 +128,14 @@ def _sm_run(t, fn, masked_fn):
     return {"y": y.detach(), "dx": x.grad}
 
 
+def _var_mean_run(t, fn):
+    x = _leaf(t["x"])
+    var, mean = fn(x, -1, 1)
+    # the first two columns of the seeded gradient tensor serve as the gradients of the outputs
+    torch.autograd.backward([var, mean], [t["dy"][:, 0].contiguous(), t["dy"][:, 1].contiguous()])
+    return {"var": var.detach(), "mean": mean.detach(), "dx": x.grad}
+
+
 # --------------------------------------------------------------------- RMSNorm / GEGLU C3
 def _c3_make(rank, world, device, scale=1, with_geglu=False, n_scale=1):
     rows, k, n, seed = 8192 // scale, 4096, 2 * 11008 // n_scale, 2
@@ -277,6 +285,15 @@ def build_workloads() -> Dict[str, Workload]:
         lambda t, ns: _attn_run(t, ns.scaled_dot_product_attention, False),
         lambda t: _attn_flops(t, False),
         ["q", "k", "v", "dy", "mask"], ["y", "dq", "dk", "dv"],
+    )
+    # beyond BASELINE.json's configurations: the row reductions on the softmax configuration's input
+    w["var_mean"] = Workload(
+        "var_mean", -1, "hbm", torch.float16, 1,
+        "VarMean fwd+bwd fp16 x[16384,4096] ~N(0,2), dim=-1, correction 1 (not a BASELINE.json config)",
+        lambda r, n, d, scale=1: _sm_make(r, n, d, scale, False),
+        lambda t, ns: _var_mean_run(t, ns.var_mean),
+        lambda t: 3.0 * _bytes(t["x"]),
+        ["x", "dy"], ["var", "mean", "dx"],
     )
     return w
 
