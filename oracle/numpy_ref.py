@@ -188,3 +188,23 @@ def attention_bwd(dout, q, k, v, mask=None, causal=False, scale=None):
     dq = scale * (ds @ k)
     dk = scale * (np.swapaxes(ds, -1, -2) @ q)
     return dq, dk, dv, ds
+
+
+def var_mean_fwd(x, axis, correction=1):
+    """sum, mean and variance along `axis` (trident/language/sum.py, mean.py, var.py: centred
+    squares divided by n - correction)."""
+    x = _f64(x)
+    n = x.shape[axis]
+    total = x.sum(axis=axis)
+    mean = total / n
+    var = ((x - np.expand_dims(mean, axis)) ** 2).sum(axis=axis) / (n - correction)
+    return total, mean, var
+
+
+def var_mean_bwd(dvar, dmean, x, axis, correction=1):
+    """dx = dvar * 2 (x - mean) / (n - correction) + dmean / n (trident/kernel/var_mean.py:86-131)."""
+    x = _f64(x)
+    n = x.shape[axis]
+    mean = np.expand_dims(x.mean(axis=axis), axis)
+    return (np.expand_dims(_f64(dvar), axis) * 2.0 * (x - mean) / (n - correction)
+            + np.expand_dims(_f64(dmean), axis) / n)

@@ -83,6 +83,17 @@ def main():
     y, (dq, dk, dv) = grads(lambda a, b_, c: torch_oracle.scaled_dot_product_attention(a, b_, c, attn_mask=mask), [q, k, v], dy)
     save("attention_masked", q=q, k=k, v=v, dy=dy, mask=mask, y=y, dq=dq, dk=dk, dv=dv)
 
+    g.manual_seed(105)
+    x = randn(g, 18, 120, mean=0.5)
+    for dim in (0, 1):
+        n_out = 120 if dim == 0 else 18
+        gv, gm = randn(g, n_out), randn(g, n_out)
+        leaf = x.clone().requires_grad_(True)
+        var, mean = torch_oracle.var_mean(leaf, dim, 1)
+        torch.autograd.backward([var, mean], [gv, gm])
+        save(f"var_mean_dim{dim}", x=x, gv=gv, gm=gm, var=var.detach(), mean=mean.detach(), dx=leaf.grad,
+             sum=torch_oracle.sum(x, dim))
+
 
 if __name__ == "__main__":
     main()

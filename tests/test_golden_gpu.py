@@ -69,3 +69,14 @@ def test_attention(device):
     g = load("attention_masked", device)
     got = run(lambda a, b, c: F.scaled_dot_product_attention(a, b, c, attn_mask=g["mask"]), [g["q"], g["k"], g["v"]], g["dy"])
     check(got, [g["y"], g["dq"], g["dk"], g["dv"]], ["y", "dq", "dk", "dv"], atol=1e-4)
+
+
+@pytest.mark.parametrize("dim", [0, 1])
+def test_var_mean_and_sum(dim, device):
+    g = load(f"var_mean_dim{dim}", device)
+    leaf = g["x"].clone().requires_grad_(True)
+    var, mean = F.var_mean(leaf, dim, 1)
+    torch.autograd.backward([var, mean], [g["gv"], g["gm"]])
+    check([var.detach(), mean.detach(), leaf.grad], [g["var"], g["mean"], g["dx"]], ["var", "mean", "dx"], atol=2e-6)
+    check([F.sum(g["x"], dim), F.mean(g["x"], dim), F.var(g["x"], dim, 1)], [g["sum"], g["mean"], g["var"]],
+          ["sum", "mean", "var"], atol=2e-5)

@@ -40,7 +40,7 @@ def test_golden_files_present():
     assert names == [
         "attention_causal", "attention_masked", "geglu", "layer_norm", "linear",
         "masked_softmax_dim0", "masked_softmax_dim1", "rms_norm_full", "rms_norm_half",
-        "softmax_dim0", "softmax_dim1",
+        "softmax_dim0", "softmax_dim1", "var_mean_dim0", "var_mean_dim1",
     ]
 
 
@@ -147,3 +147,18 @@ def test_rms_norm_derivative_is_exact():
         xm[idx] -= h
         fd = ((numpy_ref.rms_norm_fwd(xp, 0.5, w, None, 1e-3)[0] - numpy_ref.rms_norm_fwd(xm, 0.5, w, None, 1e-3)[0]) * dy).sum() / (2 * h)
         assert abs(fd - dx[idx]) < 1e-6
+
+
+@pytest.mark.parametrize("dim", [0, 1])
+def test_var_mean(dim):
+    g = load(f"var_mean_dim{dim}")
+    leaf = t(g["x"]).clone().requires_grad_(True)
+    var, mean = torch_oracle.var_mean(leaf, dim, 1)
+    torch.autograd.backward([var, mean], [t(g["gv"]), t(g["gm"])])
+    for a, b in ((var.detach().numpy(), g["var"]), (mean.detach().numpy(), g["mean"]), (leaf.grad.numpy(), g["dx"])):
+        near(a, b, 2e-6)
+    total, mean_n, var_n = numpy_ref.var_mean_fwd(g["x"], dim, 1)
+    near(total, g["sum"], 2e-5)
+    near(mean_n, g["mean"])
+    near(var_n, g["var"])
+    near(numpy_ref.var_mean_bwd(g["gv"], g["gm"], g["x"], dim, 1), g["dx"])
