@@ -54,6 +54,9 @@ def test_modules_and_reprs():
     assert gg.bias is None and gg.weight.abs().max() <= 0.25
     assert "dim=1, backend=Trident" in repr(trident.Softmax(1))
     assert "dim=None, backend=Trident" in repr(trident.MaskedSoftmax())
+    assert "dim=0, backend=Trident" in repr(trident.Sum(0)) and "dim=1, backend=Trident" in repr(trident.Mean(1))
+    assert "dim=1, correction=0, backend=Trident" in repr(trident.Var(1, 0))
+    assert "dim=None, correction=1, backend=Trident" in repr(trident.VarMean())
     assert trident.use_trace is False and trident.use_autotune is True
 
 
@@ -79,6 +82,10 @@ def test_no_cpu_fallback():
         trident.function.softmax(x, 1)
     with pytest.raises(_lib.Tb200Error, match="CUDA tensors only"):
         trident.function.layer_norm(x, (8,))
+    with pytest.raises(_lib.Tb200Error, match="CUDA tensors only"):
+        trident.function.var_mean(x, 1)
+    with pytest.raises(_lib.Tb200Error, match="CUDA tensors only"):
+        trident.function.sum(x, 0)
 
 
 def test_dtype_code():

@@ -1132,9 +1132,16 @@ static int launch_grouped(const GroupedPlan& gp, T* dx, float* partial, const T*
     }
     int cols_i = (int)cols, pc_i = (int)partial_cols, wc_i = want_cols ? 1 : 0, slab = 0;
     if (fuse && want_cols && g_norm_fused_finalize) {
-      int per_sm = 0;
-      if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, 512, smem) == cudaSuccess &&
-          (int64_t)per_sm * sm_count() >= grid) {
+      // (the occupancy of one kernel instantiation depends on the shared-memory size only: cached)
+      static thread_local size_t cached_smem = ~size_t(0);
+      static thread_local int cached_per_sm = 0;
+      if (cached_smem != smem) {
+        int q = 0;
+        cached_per_sm = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&q, kern, 512, smem) == cudaSuccess ? q : 0;
+        cached_smem = smem;
+      }
+      const int per_sm = cached_per_sm;
+      if ((int64_t)per_sm * sm_count() >= grid) {
         const int64_t limit = db_out ? 2 * cols : cols;
         slab = 16;
         while (slab < 64 && ceil_div(limit, slab) > grid) slab *= 2;
