@@ -13,13 +13,19 @@
 //     B: dS^T = P^T (dP^T - delta_q)                   -> 16-bit, over dP^T and to smem
 //   dV  += P^T  dO_i            (A from TMEM, B = dO_i read MN-major)    -> TMEM [kv][d]
 //   dK  += dS^T Q_i             (A from TMEM, B = Q_i  read MN-major)    -> TMEM [kv][d]
-//   dQ_i = dS K_j               (A = dS^T in smem read MN-major, B = K_j MN-major)
-//                               -> TMEM [q][d], in the columns dP^T occupied
-//   drain warps (one thread per query row) move dQ_i from tensor memory into the shared
-//   memory that Q_i and dO_i occupied (free once dK has consumed Q_i), and one thread adds it
-//   to an fp32 accumulator in global memory with bulk tensor reduce-add copies (the
-//   per-thread vector reductions this replaces were bound by uncoalesced 16-byte atomics);
-//   a last small kernel scales and rounds the accumulator.
+//   dQ_i, in the columns dP^T occupied, by head size:
+//     D = 128: dQ_i^T = K_j^T dS^T (A = K_j, B = dS^T in smem, both MN-major) -> TMEM [d][q]; the
+//              drain warps (one thread per feature d) add it to an fp32 accumulator in global
+//              memory with red.global.add.f32, a warp covering 128 contiguous bytes of one dQ
+//              row per instruction. Three of the four 32-column blocks are loaded before the
+//              first reductions, so 32 of the 128 reductions per thread precede the release of
+//              the tensor memory (the next dP^T needs those columns).
+//     D = 64:  dQ_i = dS K_j (A = dS^T in smem, B = K_j, both MN-major) -> TMEM [q][d]; the drain
+//              warps (one thread per query row) copy it into a staging tile of its own in shared
+//              memory and one thread adds that to the accumulator with bulk tensor reduce-add
+//              copies. (Per-thread 16-byte reductions of this layout were bound by half-used
+//              L2 sectors; M = 64 products for a transposed dQ are not used.)
+//   A last small kernel scales and rounds the accumulator.
 //
 // The MMA thread issues, per query tile s:  dP^T(s) | dV(s) | S^T(s+1) | dK(s) dQ(s), so the
 // tensor pipe always has the neighbouring tile's products to run while the compute warps are

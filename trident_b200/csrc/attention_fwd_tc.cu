@@ -11,8 +11,11 @@
 //               O_t += P_t V_j (P_t read from tensor memory, V_j MN-major in smem)
 //   warp 2      tensor-memory allocation
 //   warps 4-7   softmax of query tile 0, warps 8-11 of query tile 1: one thread per score
-//               row; row maximum and sum need no shuffles. exp2 with the softmax scale and
-//               log2(e) folded in; P is written back over S as packed 16-bit values.
+//               row; row maximum and sum need no shuffles. The 128 scores of the row are read
+//               from tensor memory once and stay in registers between the maximum and the
+//               exponentials (the softmax warps raise their register allowance with setmaxnreg,
+//               the four service warps lower theirs). exp2 with the softmax scale and log2(e)
+//               folded in; P is written back over S as packed 16-bit values.
 //
 // The running maximum used for the exponent is only advanced when the true maximum has
 // moved by more than 8 (in log2 units); only then is the accumulator O_t rescaled in tensor
