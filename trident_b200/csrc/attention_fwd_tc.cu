@@ -40,6 +40,10 @@ namespace {
 constexpr int TQ = 128;       // query rows per tile
 constexpr int TK = 128;        // key/value rows per tile
 constexpr int FWD_THREADS = 384;
+// Register allowances of the kernel's warps (see the setmaxnreg calls): the kernel must be launched
+// with REGS_LAUNCH registers per thread for the totals to fit the CTA's pool; the host checks the
+// compiled kernel's register count before the first launch.
+constexpr int REGS_LAUNCH = 168, REGS_SERVICE = 48, REGS_SOFTMAX = 224;
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr float LN2 = 0.6931471805599453f;
 constexpr float RESCALE_THRESHOLD = 8.f;
@@ -188,7 +192,6 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
   // (two warpgroups) take them. An increase waits, without a bound, until the CTA's own pool
   // (the registers it was launched with) holds enough, so the totals are checked at compile
   // time: a sum above the launch allocation would block the softmax warps for ever.
-  constexpr int REGS_LAUNCH = 168, REGS_SERVICE = 48, REGS_SOFTMAX = 224;
   static_assert(FWD_THREADS == 384 && REGS_LAUNCH * FWD_THREADS <= 65536, "launch allocation");
   static_assert(4 * 32 * REGS_SERVICE + 8 * 32 * REGS_SOFTMAX <= REGS_LAUNCH * FWD_THREADS,
                 "register pool of the CTA exceeded: setmaxnreg.inc would never return");
@@ -581,10 +584,22 @@ static int launch_fwd(const CUtensorMap& mq, const CUtensorMap& mk, const CUtens
   auto kern = attn_fwd_tc_kernel<T, D, CAUSAL, MASKED>;
   static std::once_flag once;
   static cudaError_t attr_err = cudaSuccess;
-  std::call_once(once, [&] { attr_err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM); });
+  static int launch_regs = 0;
+  std::call_once(once, [&] {
+    attr_err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+    cudaFuncAttributes fa;
+    if (attr_err == cudaSuccess && (attr_err = cudaFuncGetAttributes(&fa, kern)) == cudaSuccess) launch_regs = fa.numRegs;
+  });
   if (attr_err != cudaSuccess) {
     set_error("attention_fwd: cudaFuncSetAttribute failed: %s", cudaGetErrorString(attr_err));
     return (int)attr_err;
+  }
+  // The kernel's setmaxnreg.inc has no bound on its wait: refuse to launch a build whose register
+  // pool (registers per thread at launch x threads) cannot hold the allowances it will ask for.
+  if (launch_regs * FWD_THREADS < 4 * 32 * REGS_SERVICE + 8 * 32 * REGS_SOFTMAX) {
+    set_error("attention_fwd: kernel compiled with %d registers per thread, the register rebalancing needs %d",
+              launch_regs, REGS_LAUNCH);
+    return TB200_ERR_UNSUPPORTED;
   }
   dim3 grid((unsigned)((p.nq + 1) / 2), (unsigned)(p.a.B * p.a.H));
   kern<<<grid, FWD_THREADS, SMEM, st>>>(mq, mk, mv, p);
