@@ -98,8 +98,9 @@ extern "C" int tb200_linear_fwd(void* y, const void* x, const void* w, const voi
                                 int64_t x_sk, int64_t w_sn, int64_t w_sk, int allow_tf32, int dtype,
                                 void* stream) {
   (void)allow_tf32;  // fp32 operands are multiplied in full fp32 on the CUDA cores
-  TB200_REQUIRE(y && x && w, TB200_ERR_INVALID, "linear_fwd: null pointer");
   if (int rc = check_dims("linear_fwd", B, M, N, K)) return rc;
+  if (B * M * N == 0) return 0;  // nothing to write (empty tensors may come with null pointers)
+  TB200_REQUIRE(y && x && w, TB200_ERR_INVALID, "linear_fwd: null pointer");
   cudaStream_t st = (cudaStream_t)stream;
   if (!force_simt()) {
     // y[(b,m), n] = sum_k x[(b,m), k] w[n, k]: batch folds into M when x is batch-collapsible
@@ -131,8 +132,9 @@ extern "C" int tb200_linear_bwd_input(void* dx, const void* dy, const void* w, i
                                       int64_t dx_sk, int64_t w_sn, int64_t w_sk, int allow_tf32,
                                       int dtype, void* stream) {
   (void)allow_tf32;
-  TB200_REQUIRE(dx && dy && w, TB200_ERR_INVALID, "linear_bwd_input: null pointer");
   if (int rc = check_dims("linear_bwd_input", B, M, N, K)) return rc;
+  if (B * M * K == 0) return 0;
+  TB200_REQUIRE(dx && dy && w, TB200_ERR_INVALID, "linear_bwd_input: null pointer");
   cudaStream_t st = (cudaStream_t)stream;
   if (!force_simt()) {
     // dx[(b,m), k] = sum_n dy[(b,m), n] w[n, k]: the reduction index n is dy's contiguous
@@ -164,8 +166,11 @@ extern "C" int tb200_linear_bwd_weight(void* dw, const void* dy, const void* x, 
                                        int64_t M, int64_t N, int64_t K, int64_t x_sb, int64_t x_sm,
                                        int64_t x_sk, int allow_tf32, int dtype, void* stream) {
   (void)allow_tf32;
-  TB200_REQUIRE(dw && dy && x, TB200_ERR_INVALID, "linear_bwd_weight: null pointer");
   if (int rc = check_dims("linear_bwd_weight", B, M, N, K)) return rc;
+  if (N * K == 0) return 0;
+  if (B * M == 0)  // a sum over no rows
+    return zero_fill(dw, (size_t)N * K * dtype_size(dtype), (cudaStream_t)stream, "linear_bwd_weight");
+  TB200_REQUIRE(dw && dy && x, TB200_ERR_INVALID, "linear_bwd_weight: null pointer");
   cudaStream_t st = (cudaStream_t)stream;
   if (!force_simt()) {
     // dw[n, k] = sum_{(b,m)} dy[(b,m), n] x[(b,m), k]: both operands are MN-major.
@@ -198,8 +203,9 @@ extern "C" int tb200_geglu_fwd(void* out, void* state_gate, const void* x, const
                                int64_t x_sb, int64_t x_sm, int64_t x_sk, int64_t w_sn, int64_t w_sk,
                                int gelu_tanh, int allow_tf32, int dtype, void* stream) {
   (void)allow_tf32;
-  TB200_REQUIRE(out && state_gate && x && w, TB200_ERR_INVALID, "geglu_fwd: null pointer");
   if (int rc = check_dims("geglu_fwd", B, M, N, K)) return rc;
+  if (B * M * N == 0) return 0;
+  TB200_REQUIRE(out && state_gate && x && w, TB200_ERR_INVALID, "geglu_fwd: null pointer");
   TB200_REQUIRE(N % 2 == 0, TB200_ERR_INVALID, "geglu_fwd: N=%lld must be even", (long long)N);
   cudaStream_t st = (cudaStream_t)stream;
   if (!force_simt()) {

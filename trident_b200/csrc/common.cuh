@@ -48,6 +48,17 @@ static inline void bind_primary_context() {
   if (cudaGetDevice(&dev) == cudaSuccess) cudaSetDevice(dev);
 }
 
+// An empty problem (no rows) launches nothing; outputs that are sums over the rows are zero.
+static inline int zero_fill(void* p, size_t bytes, cudaStream_t st, const char* who) {
+  if (!p || bytes == 0) return 0;
+  cudaError_t e = cudaMemsetAsync(p, 0, bytes, st);
+  if (e != cudaSuccess) {
+    set_error("%s: cudaMemsetAsync failed: %s", who, cudaGetErrorString(e));
+    return (int)e;
+  }
+  return 0;
+}
+
 static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 static inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
 static inline size_t dtype_size(int dtype) { return dtype == TB200_F32 ? 4 : 2; }

@@ -345,8 +345,10 @@ extern "C" size_t tb200_linear_bwd_bias_workspace(int64_t rows, int64_t N) {
 extern "C" int tb200_linear_bwd_bias(void* dbias, const void* dy, void* workspace,
                                      size_t workspace_bytes, int64_t rows, int64_t N, int dtype,
                                      void* stream) {
-  TB200_REQUIRE(dbias && dy && workspace, TB200_ERR_INVALID, "linear_bwd_bias: null pointer");
   TB200_REQUIRE(rows >= 0 && N > 0, TB200_ERR_INVALID, "linear_bwd_bias: bad shape");
+  if (rows == 0)  // a sum over no rows
+    return zero_fill(dbias, (size_t)N * dtype_size(dtype), (cudaStream_t)stream, "linear_bwd_bias");
+  TB200_REQUIRE(dbias && dy && workspace, TB200_ERR_INVALID, "linear_bwd_bias: null pointer");
   cudaStream_t st = (cudaStream_t)stream;
   const int64_t slabs = bias_slabs(rows, N);
   TB200_REQUIRE(workspace_bytes >= (size_t)slabs * N * sizeof(float), TB200_ERR_WORKSPACE,
@@ -380,11 +382,11 @@ extern "C" int tb200_linear_bwd_bias(void* dbias, const void* dy, void* workspac
 extern "C" int tb200_geglu_bwd_elementwise(void* d_state_gate, const void* dout,
                                            const void* state_gate, int64_t rows, int64_t N,
                                            int gelu_tanh, int dtype, void* stream) {
-  TB200_REQUIRE(d_state_gate && dout && state_gate, TB200_ERR_INVALID,
-                "geglu_bwd_elementwise: null pointer");
   TB200_REQUIRE(rows >= 0 && N > 0 && N % 2 == 0, TB200_ERR_INVALID,
                 "geglu_bwd_elementwise: N must be even and positive");
   if (rows == 0) return 0;
+  TB200_REQUIRE(d_state_gate && dout && state_gate, TB200_ERR_INVALID,
+                "geglu_bwd_elementwise: null pointer");
   cudaStream_t st = (cudaStream_t)stream;
   const int64_t X = N / 2;
   return dispatch_dtype(dtype, [&](auto tag) -> int {
@@ -412,10 +414,12 @@ extern "C" int tb200_geglu_bwd_elementwise_bias(void* d_state_gate, void* dbias,
                                                 const void* state_gate, void* workspace,
                                                 size_t workspace_bytes, int64_t rows, int64_t N,
                                                 int gelu_tanh, int dtype, void* stream) {
-  TB200_REQUIRE(d_state_gate && dbias && dout && state_gate && workspace, TB200_ERR_INVALID,
-                "geglu_bwd_elementwise_bias: null pointer");
   TB200_REQUIRE(rows >= 0 && N > 0 && N % 2 == 0, TB200_ERR_INVALID,
                 "geglu_bwd_elementwise_bias: N must be even and positive");
+  if (rows == 0)  // a sum over no rows
+    return zero_fill(dbias, (size_t)N * dtype_size(dtype), (cudaStream_t)stream, "geglu_bwd_elementwise_bias");
+  TB200_REQUIRE(d_state_gate && dbias && dout && state_gate && workspace, TB200_ERR_INVALID,
+                "geglu_bwd_elementwise_bias: null pointer");
   cudaStream_t st = (cudaStream_t)stream;
   const int64_t X = N / 2;
   const int64_t slabs = bias_slabs(rows, N);

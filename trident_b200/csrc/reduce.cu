@@ -225,11 +225,11 @@ using namespace tb200;
 extern "C" int tb200_reduce_fwd(void* out_a, void* out_b, const void* x, int64_t y_size, int64_t x_size,
                                 int64_t y_stride, int64_t x_stride, int kind, float correction, int dtype,
                                 void* stream) {
-  TB200_REQUIRE(out_a && x, TB200_ERR_INVALID, "reduce_fwd: null pointer");
   TB200_REQUIRE(kind >= RK_SUM && kind <= RK_VAR_MEAN, TB200_ERR_INVALID, "reduce_fwd: unknown kind %d", kind);
-  TB200_REQUIRE(kind != RK_VAR_MEAN || out_b, TB200_ERR_INVALID, "reduce_fwd: var_mean needs two outputs");
   TB200_REQUIRE(y_size >= 0 && x_size > 0, TB200_ERR_INVALID, "reduce_fwd: bad shape");
   if (y_size == 0) return 0;
+  TB200_REQUIRE(out_a && x, TB200_ERR_INVALID, "reduce_fwd: null pointer");
+  TB200_REQUIRE(kind != RK_VAR_MEAN || out_b, TB200_ERR_INVALID, "reduce_fwd: var_mean needs two outputs");
   cudaStream_t st = (cudaStream_t)stream;
   return dispatch_dtype(dtype, [&](auto tag) -> int {
     using T = decltype(tag);
@@ -260,11 +260,11 @@ extern "C" int tb200_reduce_fwd(void* out_a, void* out_b, const void* x, int64_t
 extern "C" int tb200_reduce_bwd(void* dx, const void* dout_a, const void* dout_b, const void* x, int64_t y_size,
                                 int64_t x_size, int64_t y_stride, int64_t x_stride, int kind, float correction,
                                 int dtype, void* stream) {
-  TB200_REQUIRE(dx && dout_a, TB200_ERR_INVALID, "reduce_bwd: null pointer");
   TB200_REQUIRE(kind >= RK_SUM && kind <= RK_VAR_MEAN, TB200_ERR_INVALID, "reduce_bwd: unknown kind %d", kind);
-  TB200_REQUIRE(kind < RK_VAR || x, TB200_ERR_INVALID, "reduce_bwd: the variance gradient needs the input");
   TB200_REQUIRE(y_size >= 0 && x_size > 0, TB200_ERR_INVALID, "reduce_bwd: bad shape");
   if (y_size == 0) return 0;
+  TB200_REQUIRE(dx && dout_a, TB200_ERR_INVALID, "reduce_bwd: null pointer");
+  TB200_REQUIRE(kind < RK_VAR || x, TB200_ERR_INVALID, "reduce_bwd: the variance gradient needs the input");
   cudaStream_t st = (cudaStream_t)stream;
   return dispatch_dtype(dtype, [&](auto tag) -> int {
     using T = decltype(tag);

@@ -448,10 +448,10 @@ using namespace tb200;
 extern "C" int tb200_layer_norm_fwd(void* y, float* mean, float* rstd, const void* x,
                                     const void* weight, const void* bias, int64_t rows,
                                     int64_t cols, float eps, int dtype, void* stream) {
-  TB200_REQUIRE(y && mean && rstd && x, TB200_ERR_INVALID, "layer_norm_fwd: null pointer");
   TB200_REQUIRE(rows >= 0 && cols > 0, TB200_ERR_INVALID, "layer_norm_fwd: bad shape %lld x %lld",
                 (long long)rows, (long long)cols);
-  if (rows == 0) return 0;
+  if (rows == 0) return 0;  // (empty tensors may come with null pointers)
+  TB200_REQUIRE(y && mean && rstd && x, TB200_ERR_INVALID, "layer_norm_fwd: null pointer");
   cudaStream_t st = (cudaStream_t)stream;
   return dispatch_dtype(dtype, [&](auto tag) -> int {
     using T = decltype(tag);
@@ -487,9 +487,13 @@ extern "C" int tb200_layer_norm_bwd(void* dx, void* dweight, void* dbias, const 
                                     const void* x, const void* weight, const float* mean,
                                     const float* rstd, void* workspace, size_t workspace_bytes,
                                     int64_t rows, int64_t cols, int dtype, void* stream) {
-  TB200_REQUIRE(dx && dy && x && mean && rstd, TB200_ERR_INVALID, "layer_norm_bwd: null pointer");
   TB200_REQUIRE(rows >= 0 && cols > 0, TB200_ERR_INVALID, "layer_norm_bwd: bad shape");
   cudaStream_t st = (cudaStream_t)stream;
+  if (rows == 0) {  // sums over no rows
+    if (int rc = zero_fill(dweight, (size_t)cols * dtype_size(dtype), st, "layer_norm_bwd")) return rc;
+    return zero_fill(dbias, (size_t)cols * dtype_size(dtype), st, "layer_norm_bwd");
+  }
+  TB200_REQUIRE(dx && dy && x && mean && rstd, TB200_ERR_INVALID, "layer_norm_bwd: null pointer");
   const bool want_cols = dweight || dbias;
   {
     bool handled = false;
@@ -548,12 +552,12 @@ extern "C" int tb200_rms_norm_fwd(void* y, float* rms, const void* x, const void
                                   const void* bias, int64_t rows, int64_t cols, int64_t row_stride,
                                   int64_t col_stride, int64_t partial_cols, float eps, int dtype,
                                   void* stream) {
-  TB200_REQUIRE(y && rms && x && weight, TB200_ERR_INVALID, "rms_norm_fwd: null pointer");
   TB200_REQUIRE(rows >= 0 && cols > 0, TB200_ERR_INVALID, "rms_norm_fwd: bad shape");
   TB200_REQUIRE(partial_cols > 0 && partial_cols <= cols, TB200_ERR_INVALID,
                 "rms_norm_fwd: partial_cols %lld outside (0, %lld]", (long long)partial_cols,
                 (long long)cols);
   if (rows == 0) return 0;
+  TB200_REQUIRE(y && rms && x && weight, TB200_ERR_INVALID, "rms_norm_fwd: null pointer");
   cudaStream_t st = (cudaStream_t)stream;
   return dispatch_dtype(dtype, [&](auto tag) -> int {
     using T = decltype(tag);
@@ -593,12 +597,16 @@ extern "C" int tb200_rms_norm_bwd(void* dx, void* dweight, void* dbias, const vo
                                   void* workspace, size_t workspace_bytes, int64_t rows,
                                   int64_t cols, int64_t row_stride, int64_t col_stride,
                                   int64_t partial_cols, float eps, int dtype, void* stream) {
-  TB200_REQUIRE(dx && dweight && dy && x && weight && rms, TB200_ERR_INVALID,
-                "rms_norm_bwd: null pointer");
   TB200_REQUIRE(rows >= 0 && cols > 0, TB200_ERR_INVALID, "rms_norm_bwd: bad shape");
   TB200_REQUIRE(partial_cols > 0 && partial_cols <= cols, TB200_ERR_INVALID,
                 "rms_norm_bwd: partial_cols outside (0, cols]");
   cudaStream_t st = (cudaStream_t)stream;
+  if (rows == 0) {  // sums over no rows
+    if (int rc = zero_fill(dweight, (size_t)cols * dtype_size(dtype), st, "rms_norm_bwd")) return rc;
+    return zero_fill(dbias, (size_t)cols * dtype_size(dtype), st, "rms_norm_bwd");
+  }
+  TB200_REQUIRE(dx && dweight && dy && x && weight && rms, TB200_ERR_INVALID,
+                "rms_norm_bwd: null pointer");
   {
     bool handled = false;
     int rc = try_rms_norm_bwd_grouped(dx, dweight, dbias, dy, x, weight, rms, workspace, workspace_bytes, rows,

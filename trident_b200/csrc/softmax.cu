@@ -151,9 +151,9 @@ extern "C" int tb200_softmax_fwd(void* y, const void* x, const uint8_t* mask, in
                                  int64_t cols, int64_t row_stride, int64_t col_stride,
                                  int64_t mask_row_stride, int64_t mask_col_stride, int dtype,
                                  void* stream) {
-  TB200_REQUIRE(y && x, TB200_ERR_INVALID, "softmax_fwd: null pointer");
   TB200_REQUIRE(rows >= 0 && cols > 0, TB200_ERR_INVALID, "softmax_fwd: bad shape");
   if (rows == 0) return 0;
+  TB200_REQUIRE(y && x, TB200_ERR_INVALID, "softmax_fwd: null pointer");
   cudaStream_t st = (cudaStream_t)stream;
   return dispatch_dtype(dtype, [&](auto tag) -> int {
     using T = decltype(tag);
@@ -192,9 +192,9 @@ extern "C" int tb200_softmax_fwd(void* y, const void* x, const uint8_t* mask, in
 extern "C" int tb200_softmax_bwd(void* dx, const void* dy, const void* y, int64_t rows,
                                  int64_t cols, int64_t row_stride, int64_t col_stride, int dtype,
                                  void* stream) {
-  TB200_REQUIRE(dx && dy && y, TB200_ERR_INVALID, "softmax_bwd: null pointer");
   TB200_REQUIRE(rows >= 0 && cols > 0, TB200_ERR_INVALID, "softmax_bwd: bad shape");
   if (rows == 0) return 0;
+  TB200_REQUIRE(dx && dy && y, TB200_ERR_INVALID, "softmax_bwd: null pointer");
   cudaStream_t st = (cudaStream_t)stream;
   return dispatch_dtype(dtype, [&](auto tag) -> int {
     using T = decltype(tag);
