@@ -500,7 +500,7 @@ def measure(wl, args, rank, world, device, with_cpu, sampler=None):
     traffic, traffic_src = NCU_TRAFFIC.get(wl.name, (None, "not captured"))
     if args.scale != 1 and traffic is not None:
         traffic = traffic / args.scale
-    e2e_steps = max(3, min(args.steps, 10))
+    e2e_steps = max(3, min(args.steps, 20))
     esecs, h2d, d2h = time_e2e(wl, tensors, e2e_steps, 1, world, device)
     e2e_value = rate(wl, work_total * e2e_steps, esecs)
     out = {
