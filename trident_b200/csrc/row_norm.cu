@@ -435,8 +435,9 @@ static size_t col_partial_bytes(int64_t cols) {
 
 template <typename T>
 static int finalize_cols(T* da, T* db, const float* partial, int nparts, int64_t cols,
-                         cudaStream_t st) {
-  dim3 grid((unsigned)ceil_div(cols, 32), 2), block(32, 32);
+                         cudaStream_t st, int sets = 2) {
+  // `sets`: 2 for partial rows [2][cols] (weight, bias), 1 for [cols] (weight only)
+  dim3 grid((unsigned)ceil_div(cols, 32), (unsigned)sets), block(32, 32);
   colsum_finalize_kernel<T><<<grid, block, 0, st>>>(da, db, partial, nparts, (int)cols);
   return launch_status("colsum_finalize");
 }
@@ -1008,8 +1009,10 @@ __global__ void __launch_bounds__(512, MINB)
       }
     }
   }
+  // partial rows are [2][cols] (weight, bias), or [cols] when no bias gradient is kept
+  constexpr int NSETS = WANT_B ? 2 : 1;
   if (want_cols) {
-    // fold the groups of this CTA in a fixed order, then write its [2, cols] partial row
+    // fold the groups of this CTA in a fixed order, then write its partial row
     for (int g = 0; g < GROUPS; ++g) {
       if (group == g) {
 #pragma unroll
@@ -1023,10 +1026,10 @@ __global__ void __launch_bounds__(512, MINB)
               if constexpr (WANT_B) am::unpack2f(acc_b[c][i >> 1], pb[0], pb[1]);
               if (g == 0) {
                 colbuf[col + i] = pw[i & 1];
-                colbuf[cols + col + i] = pb[i & 1];
+                if constexpr (WANT_B) colbuf[cols + col + i] = pb[i & 1];
               } else {
                 colbuf[col + i] += pw[i & 1];
-                colbuf[cols + col + i] += pb[i & 1];
+                if constexpr (WANT_B) colbuf[cols + col + i] += pb[i & 1];
               }
             }
           }
@@ -1034,8 +1037,8 @@ __global__ void __launch_bounds__(512, MINB)
       }
       __syncthreads();
     }
-    float* out = partial + (int64_t)blockIdx.x * 2 * cols;
-    for (int i = threadIdx.x * 4; i < 2 * cols; i += 512 * 4)
+    float* out = partial + (int64_t)blockIdx.x * NSETS * cols;
+    for (int i = threadIdx.x * 4; i < NSETS * cols; i += 512 * 4)
       *reinterpret_cast<float4*>(out + i) = *reinterpret_cast<const float4*>(colbuf + i);
   }
   if (fused_slab > 0) {
@@ -1048,7 +1051,7 @@ __global__ void __launch_bounds__(512, MINB)
     const int nparts = gridDim.x;
     const int lanes = 512 / fused_slab;
     const int cl = threadIdx.x % fused_slab, j = threadIdx.x / fused_slab;
-    const int limit = db_out ? 2 * cols : cols;
+    const int limit = (WANT_B && db_out) ? 2 * cols : cols;
     for (int base = blockIdx.x * fused_slab; base < limit; base += gridDim.x * fused_slab) {
       const int cc = base + cl;
       float acc = 0.f;
@@ -1058,7 +1061,7 @@ __global__ void __launch_bounds__(512, MINB)
 #pragma unroll
           for (int u = 0; u < 8; ++u) {
             const int p = p0 + lanes * u;
-            v[u] = p < nparts ? __ldcg(partial + (int64_t)p * 2 * cols + cc) : 0.f;
+            v[u] = p < nparts ? __ldcg(partial + (int64_t)p * NSETS * cols + cc) : 0.f;
           }
 #pragma unroll
           for (int u = 0; u < 8; ++u) acc += v[u];
@@ -1251,7 +1254,7 @@ int try_rms_norm_bwd_grouped(void* dx, void* dweight, void* dbias, const void* d
                                                     (T*)dbias, &fused);
     if (rc) return rc;
     if (!fused) {
-      rc = finalize_cols<T>((T*)dweight, (T*)dbias, (const float*)workspace, nparts, cols, st);
+      rc = finalize_cols<T>((T*)dweight, (T*)dbias, (const float*)workspace, nparts, cols, st, dbias ? 2 : 1);
       if (rc) return rc;
     }
     note_kernel("row_vec", fused ? 1 : 2);
