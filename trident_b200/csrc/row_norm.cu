@@ -1019,17 +1019,30 @@ __global__ void __launch_bounds__(512, MINB)
         for (int c = 0; c < CHUNKS; ++c) {
           const int col = (c * TPR + tid) * VEC;
           if (col < cols) {
+            // 16-byte shared-memory accesses (col is a multiple of VEC, VEC of 4)
+            float vw[VEC], vb[VEC];
 #pragma unroll
-            for (int i = 0; i < VEC; ++i) {
-              float pw[2], pb[2] = {0.f, 0.f};
-              am::unpack2f(acc_w[c][i >> 1], pw[0], pw[1]);
-              if constexpr (WANT_B) am::unpack2f(acc_b[c][i >> 1], pb[0], pb[1]);
-              if (g == 0) {
-                colbuf[col + i] = pw[i & 1];
-                if constexpr (WANT_B) colbuf[cols + col + i] = pb[i & 1];
-              } else {
-                colbuf[col + i] += pw[i & 1];
-                if constexpr (WANT_B) colbuf[cols + col + i] += pb[i & 1];
+            for (int i = 0; i < VEC; i += 2) {
+              am::unpack2f(acc_w[c][i >> 1], vw[i], vw[i + 1]);
+              if constexpr (WANT_B) am::unpack2f(acc_b[c][i >> 1], vb[i], vb[i + 1]);
+            }
+#pragma unroll
+            for (int i = 0; i < VEC; i += 4) {
+              float4* pw4 = reinterpret_cast<float4*>(colbuf + col + i);
+              float4 a = make_float4(vw[i], vw[i + 1], vw[i + 2], vw[i + 3]);
+              if (g != 0) {
+                const float4 o = *pw4;
+                a = make_float4(o.x + a.x, o.y + a.y, o.z + a.z, o.w + a.w);
+              }
+              *pw4 = a;
+              if constexpr (WANT_B) {
+                float4* pb4 = reinterpret_cast<float4*>(colbuf + cols + col + i);
+                float4 b4 = make_float4(vb[i], vb[i + 1], vb[i + 2], vb[i + 3]);
+                if (g != 0) {
+                  const float4 o = *pb4;
+                  b4 = make_float4(o.x + b4.x, o.y + b4.y, o.z + b4.z, o.w + b4.w);
+                }
+                *pb4 = b4;
               }
             }
           }
@@ -1056,15 +1069,16 @@ __global__ void __launch_bounds__(512, MINB)
       const int cc = base + cl;
       float acc = 0.f;
       if (cc < limit) {
-        for (int p0 = j; p0 < nparts; p0 += lanes * 8) {
-          float v[8];
+        // sixteen independent loads per trip: one round trip to L2 covers up to 16 * lanes partial rows
+        for (int p0 = j; p0 < nparts; p0 += lanes * 16) {
+          float v[16];
 #pragma unroll
-          for (int u = 0; u < 8; ++u) {
+          for (int u = 0; u < 16; ++u) {
             const int p = p0 + lanes * u;
             v[u] = p < nparts ? __ldcg(partial + (int64_t)p * NSETS * cols + cc) : 0.f;
           }
 #pragma unroll
-          for (int u = 0; u < 8; ++u) acc += v[u];
+          for (int u = 0; u < 16; ++u) acc += v[u];
         }
       }
       red[j * fused_slab + cl] = acc;
