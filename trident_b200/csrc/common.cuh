@@ -59,6 +59,30 @@ static inline int zero_fill(void* p, size_t bytes, cudaStream_t st, const char* 
   return 0;
 }
 
+// Programmatic dependent launch: the kernel may be scheduled while the previous kernel of the
+// stream is still running (its launch latency and the start of its CTAs then overlap that
+// kernel's tail). A kernel launched this way must execute pdl_wait() before its first access to
+// global memory: the wait returns once the previous kernel has completed and its writes are
+// visible (and immediately when there is no such dependency). pdl_release() lets the next kernel
+// of the stream be scheduled early in the same way.
+template <typename... KArgs, typename... Args>
+static inline cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                                     bool cooperative, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  attr[1].id = cudaLaunchAttributeCooperative;
+  attr[1].val.cooperative = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = cooperative ? 2 : 1;
+  return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
+
 static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 static inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
 static inline size_t dtype_size(int dtype) { return dtype == TB200_F32 ? 4 : 2; }
@@ -146,6 +170,9 @@ __device__ inline uint4 pack<__nv_bfloat16>(const float* in) {
   for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(in[2 * i], in[2 * i + 1]);
   return r;
 }
+
+__device__ inline void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ inline void pdl_release() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 // Streaming 16-byte accesses: data is touched once, keep it out of L1.
 __device__ inline uint4 ld_stream(const void* p) {

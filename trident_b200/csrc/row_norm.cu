@@ -52,6 +52,8 @@ __global__ void __launch_bounds__(CTA_ROW ? 512 : 256, CTA_ROW ? 2 : 4)
   int phase = 0;
   RowThread<CTA_ROW> rt;
   const float inv_n = 1.f / (float)cols;
+  pdl_wait();     // (programmatic dependent launch: nothing is read before the previous kernel is done)
+  pdl_release();  // the next kernel of the stream may be scheduled
   for (int64_t row = rt.first_row(); row < rows; row += rt.row_step()) {
     uint4 raw[CHUNKS];
     const T* xr = x + row * cols;
@@ -269,6 +271,8 @@ __global__ void __launch_bounds__(CTA_ROW ? 512 : 256, CTA_ROW ? 2 : 4)
   __shared__ float slot[64];
   int phase = 0;
   RowThread<CTA_ROW> rt;
+  pdl_wait();     // (programmatic dependent launch: nothing is read before the previous kernel is done)
+  pdl_release();  // the next kernel of the stream may be scheduled
   for (int64_t row = rt.first_row(); row < rows; row += rt.row_step()) {
     constexpr bool EARLY = CHUNKS <= 4;  // as far as the registers allow
     uint4 raw[CHUNKS], wraw[EARLY ? CHUNKS : 1];
@@ -462,10 +466,10 @@ extern "C" int tb200_layer_norm_fwd(void* y, float* mean, float* rstd, const voi
     if (p.vec) {
       const int64_t grid = ceil_div(rows, p.rows_per_cta);
       int rc = dispatch_plan<T>(p, [&](auto c, auto cta) -> int {
-        ln_fwd_vec<T, decltype(c)::value, decltype(cta)::value>
-            <<<(unsigned)grid, p.threads, 0, st>>>((T*)y, mean, rstd, (const T*)x,
-                                                   (const T*)weight, (const T*)bias, rows,
-                                                   (int)cols, eps);
+        cudaError_t e = launch_pdl(ln_fwd_vec<T, decltype(c)::value, decltype(cta)::value>, dim3((unsigned)grid),
+                                   dim3(p.threads), 0, st, false, (T*)y, mean, rstd, (const T*)x, (const T*)weight,
+                                   (const T*)bias, rows, (int)cols, eps);
+        (void)e;  // picked up by launch_status
         return launch_status("ln_fwd_vec");
       });
       if (rc == 0) note_kernel("row_vec", 1);
@@ -570,10 +574,10 @@ extern "C" int tb200_rms_norm_fwd(void* y, float* rms, const void* x, const void
     if (p.vec) {
       const int64_t grid = ceil_div(rows, p.rows_per_cta);
       int rc = dispatch_plan<T>(p, [&](auto c, auto cta) -> int {
-        rms_fwd_vec<T, decltype(c)::value, decltype(cta)::value>
-            <<<(unsigned)grid, p.threads, 0, st>>>((T*)y, rms, (const T*)x, (const T*)weight,
-                                                   (const T*)bias, rows, (int)cols, row_stride,
-                                                   (int)partial_cols, eps);
+        cudaError_t e = launch_pdl(rms_fwd_vec<T, decltype(c)::value, decltype(cta)::value>, dim3((unsigned)grid),
+                                   dim3(p.threads), 0, st, false, (T*)y, rms, (const T*)x, (const T*)weight,
+                                   (const T*)bias, rows, (int)cols, row_stride, (int)partial_cols, eps);
+        (void)e;  // picked up by launch_status
         return launch_status("rms_fwd_vec");
       });
       if (rc == 0) note_kernel("row_vec", 1);
@@ -859,6 +863,8 @@ __global__ void __launch_bounds__(512, MINB)
   // loaded once, packed; with two they are re-read per pass (L1 hits).
   constexpr bool W_REGS = CHUNKS == 1 || MINB == 1;
   constexpr int PAIRS = VEC / 2;  // arithmetic runs on fp32 pairs (two-lane instructions)
+  pdl_wait();     // (programmatic dependent launch: nothing is read before the previous kernel is done)
+  pdl_release();  // the next kernel of the stream may be scheduled
   uint64_t acc_w[CHUNKS][PAIRS], acc_b[WANT_B ? CHUNKS : 1][PAIRS];
   uint4 wreg[CHUNKS];
 #pragma unroll
@@ -1173,9 +1179,15 @@ static int launch_grouped(const GroupedPlan& gp, T* dx, float* partial, const T*
       }
     }
     if (slab > 0) {
-      void* args[] = {&dx, &partial, &dy, &x, &w, &stat_a, &stat_b, &rows, &cols_i, &x_row_stride,
-                      &pc_i, &eps, &wc_i, &dw_out, &db_out, &slab};
-      cudaError_t e = cudaLaunchCooperativeKernel((const void*)kern, dim3((unsigned)grid), dim3(512), args, smem, st);
+      // cooperative, and allowed to be scheduled during the tail of the previous kernel
+      cudaError_t e = launch_pdl(kern, dim3((unsigned)grid), dim3(512), smem, st, true, dx, partial, dy, x, w, stat_a,
+                                 stat_b, rows, cols_i, x_row_stride, pc_i, eps, wc_i, dw_out, db_out, slab);
+      if (e != cudaSuccess) {  // the combination of attributes is refused: cooperative alone
+        (void)cudaGetLastError();
+        void* args[] = {&dx, &partial, &dy, &x, &w, &stat_a, &stat_b, &rows, &cols_i, &x_row_stride,
+                        &pc_i, &eps, &wc_i, &dw_out, &db_out, &slab};
+        e = cudaLaunchCooperativeKernel((const void*)kern, dim3((unsigned)grid), dim3(512), args, smem, st);
+      }
       if (e == cudaSuccess) {
         if (fused) *fused = true;
         return launch_status("norm_bwd_grouped");
@@ -1183,8 +1195,9 @@ static int launch_grouped(const GroupedPlan& gp, T* dx, float* partial, const T*
       (void)cudaGetLastError();  // fall through to the plain launch
       slab = 0;
     }
-    kern<<<(unsigned)grid, 512, smem, st>>>(dx, partial, dy, x, w, stat_a, stat_b, rows, cols_i, x_row_stride, pc_i,
-                                            eps, wc_i, (T*)nullptr, (T*)nullptr, 0);
+    cudaError_t e = launch_pdl(kern, dim3((unsigned)grid), dim3(512), smem, st, false, dx, partial, dy, x, w, stat_a,
+                               stat_b, rows, cols_i, x_row_stride, pc_i, eps, wc_i, (T*)nullptr, (T*)nullptr, 0);
+    (void)e;  // picked up by launch_status
     return launch_status("norm_bwd_grouped");
   };
 #define TB200_GROUPED_CASE(C, R, D, M)                                                      \

@@ -19,6 +19,8 @@ __global__ void __launch_bounds__(CTA_ROW ? 512 : 256)
   __shared__ float slot[64];
   int phase = 0;
   RowThread<CTA_ROW> rt;
+  pdl_wait();     // (programmatic dependent launch: nothing is read before the previous kernel is done)
+  pdl_release();  // the next kernel of the stream may be scheduled
   for (int64_t row = rt.first_row(); row < rows; row += rt.row_step()) {
     float xs[CHUNKS][VEC];
     load_row<T, CHUNKS, CTA_ROW>(xs, x + row * row_stride, cols, rt, -INFINITY);
@@ -108,6 +110,8 @@ __global__ void __launch_bounds__(CTA_ROW ? 512 : 256)
   __shared__ float slot[64];
   int phase = 0;
   RowThread<CTA_ROW> rt;
+  pdl_wait();     // (programmatic dependent launch: nothing is read before the previous kernel is done)
+  pdl_release();  // the next kernel of the stream may be scheduled
   for (int64_t row = rt.first_row(); row < rows; row += rt.row_step()) {
     float ys[CHUNKS][VEC], gs[CHUNKS][VEC];
     load_row<T, CHUNKS, CTA_ROW>(ys, y + row * row_stride, cols, rt);
@@ -169,12 +173,14 @@ extern "C" int tb200_softmax_fwd(void* y, const void* x, const uint8_t* mask, in
       int rc = dispatch_plan<T>(p, [&](auto c, auto cta) -> int {
         constexpr int C = decltype(c)::value;
         constexpr bool R = decltype(cta)::value;
+        cudaError_t e;
         if (mask)
-          softmax_fwd_vec<T, C, R, true><<<(unsigned)grid, p.threads, 0, st>>>(
-              (T*)y, (const T*)x, mask, rows, (int)cols, row_stride, mask_row_stride);
+          e = launch_pdl(softmax_fwd_vec<T, C, R, true>, dim3((unsigned)grid), dim3(p.threads), 0, st, false, (T*)y,
+                         (const T*)x, mask, rows, (int)cols, row_stride, mask_row_stride);
         else
-          softmax_fwd_vec<T, C, R, false><<<(unsigned)grid, p.threads, 0, st>>>(
-              (T*)y, (const T*)x, nullptr, rows, (int)cols, row_stride, 0);
+          e = launch_pdl(softmax_fwd_vec<T, C, R, false>, dim3((unsigned)grid), dim3(p.threads), 0, st, false, (T*)y,
+                         (const T*)x, (const uint8_t*)nullptr, rows, (int)cols, row_stride, (int64_t)0);
+        (void)e;  // picked up by launch_status
         return launch_status("softmax_fwd_vec");
       });
       if (rc == 0) note_kernel("row_vec", 1);
@@ -205,9 +211,10 @@ extern "C" int tb200_softmax_bwd(void* dx, const void* dy, const void* y, int64_
     if (p.vec) {
       const int64_t grid = ceil_div(rows, p.rows_per_cta);
       int rc = dispatch_plan<T>(p, [&](auto c, auto cta) -> int {
-        softmax_bwd_vec<T, decltype(c)::value, decltype(cta)::value>
-            <<<(unsigned)grid, p.threads, 0, st>>>((T*)dx, (const T*)dy, (const T*)y, rows,
-                                                   (int)cols, row_stride);
+        cudaError_t e = launch_pdl(softmax_bwd_vec<T, decltype(c)::value, decltype(cta)::value>, dim3((unsigned)grid),
+                                   dim3(p.threads), 0, st, false, (T*)dx, (const T*)dy, (const T*)y, rows, (int)cols,
+                                   row_stride);
+        (void)e;  // picked up by launch_status
         return launch_status("softmax_bwd_vec");
       });
       if (rc == 0) note_kernel("row_vec", 1);
