@@ -22,6 +22,25 @@ namespace tb200 {
 
 enum ReduceKind { RK_SUM = 0, RK_MEAN = 1, RK_VAR = 2, RK_VAR_MEAN = 3 };
 
+// Sums two values over the threads of a row with one shared-memory exchange (slot: [2][32] pairs).
+template <bool CTA_ROW>
+__device__ inline void row_reduce2(float& a, float& b, float* slot, int& phase) {
+  a = warp_sum(a);
+  b = warp_sum(b);
+  if constexpr (CTA_ROW) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+    float* s = slot + phase * 32;
+    phase ^= 1;
+    if (lane == 0) {
+      s[warp] = a;
+      s[16 + warp] = b;
+    }
+    __syncthreads();
+    a = warp_sum(lane < nwarps ? s[lane] : 0.f);
+    b = warp_sum(lane < nwarps ? s[16 + lane] : 0.f);
+  }
+}
+
 template <typename T, int CHUNKS, bool CTA_ROW, int KIND>
 __global__ void __launch_bounds__(CTA_ROW ? 512 : 256)
     reduce_fwd_vec(T* __restrict__ out_a, T* __restrict__ out_b, const T* __restrict__ x, int64_t rows,
@@ -40,23 +59,24 @@ __global__ void __launch_bounds__(CTA_ROW ? 512 : 256)
       const int col = rt.template col<VEC>(c);
       raw[c] = col < cols ? ld_stream(xr + col) : make_uint4(0, 0, 0, 0);
     }
-    uint64_t s2 = 0ull;
+    if constexpr (KIND == RK_SUM || KIND == RK_MEAN) {
+      uint64_t s2 = 0ull;
 #pragma unroll
-    for (int c = 0; c < CHUNKS; ++c) {
-      uint64_t t[PAIRS];
-      unpack2<T>(raw[c], t);
+      for (int c = 0; c < CHUNKS; ++c) {
+        uint64_t t[PAIRS];
+        unpack2<T>(raw[c], t);
 #pragma unroll
-      for (int i = 0; i < PAIRS; ++i) s2 = am::add2(s2, t[i]);
-    }
-    const float s = row_reduce<CTA_ROW, false>(hsum2(s2), slot, phase);
-    if constexpr (KIND == RK_SUM) {
-      if (rt.tid == 0) out_a[row] = Traits<T>::from_f(s);
-    } else if constexpr (KIND == RK_MEAN) {
-      if (rt.tid == 0) out_a[row] = Traits<T>::from_f(s / n);
+        for (int i = 0; i < PAIRS; ++i) s2 = am::add2(s2, t[i]);
+      }
+      const float s = row_reduce<CTA_ROW, false>(hsum2(s2), slot, phase);
+      if (rt.tid == 0) out_a[row] = Traits<T>::from_f(KIND == RK_SUM ? s : s / n);
     } else {
-      const float mu = s / n;
-      const uint64_t nmu2 = splat2(-mu);
-      uint64_t v2 = 0ull;
+      // Variance in one pass over the registers and one exchange: sums of d = x - c and of d^2 with
+      // the shift c = first element of the row (a sample of the row, so d is of the order of the
+      // spread and the subtraction below does not cancel): mean = c + S1/n, var = (S2 - S1^2/n)/(n-k).
+      const float shift = Traits<T>::to_f(__ldg(xr));
+      const uint64_t nshift2 = splat2(-shift);
+      uint64_t s1 = 0ull, s2 = 0ull;
 #pragma unroll
       for (int c = 0; c < CHUNKS; ++c) {
         if (rt.template col<VEC>(c) < cols) {
@@ -64,15 +84,17 @@ __global__ void __launch_bounds__(CTA_ROW ? 512 : 256)
           unpack2<T>(raw[c], t);
 #pragma unroll
           for (int i = 0; i < PAIRS; ++i) {
-            const uint64_t d = am::add2(t[i], nmu2);
-            v2 = am::fma2(d, d, v2);
+            const uint64_t d = am::add2(t[i], nshift2);
+            s1 = am::add2(s1, d);
+            s2 = am::fma2(d, d, s2);
           }
         }
       }
-      const float v = row_reduce<CTA_ROW, false>(hsum2(v2), slot, phase);
+      float a1 = hsum2(s1), a2 = hsum2(s2);
+      row_reduce2<CTA_ROW>(a1, a2, slot, phase);
       if (rt.tid == 0) {
-        out_a[row] = Traits<T>::from_f(v / (n - correction));
-        if constexpr (KIND == RK_VAR_MEAN) out_b[row] = Traits<T>::from_f(mu);
+        out_a[row] = Traits<T>::from_f((a2 - a1 * a1 / n) / (n - correction));
+        if constexpr (KIND == RK_VAR_MEAN) out_b[row] = Traits<T>::from_f(shift + a1 / n);
       }
     }
   }
