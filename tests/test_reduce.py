@@ -116,3 +116,18 @@ def test_strided_input(device):
 def test_rejects_other_ranks(device):
     with pytest.raises(ValueError):
         trident.function.sum(torch.zeros(2, 3, 4, device=device), 1)
+
+
+def test_variance_with_outlier_and_large_mean(device):
+    """The one-pass variance shifts by a sample of the row: an outlier in the first position and a
+    mean far from zero must not cost accuracy."""
+    x = util.randn(16, 4096, seed=21) * 0.5 + 300.0
+    x[:, 0] = 1.0e4
+    got_v, got_m = trident.function.var_mean(x.to(device), 1, 1)
+    want_v, want_m = torch.var_mean(x.double(), 1, correction=1)
+    assert torch.allclose(got_v.cpu().double(), want_v, rtol=2e-5, atol=0), (got_v.cpu().double() - want_v).abs().max()
+    assert torch.allclose(got_m.cpu().double(), want_m, rtol=1e-6, atol=0)
+    y = util.randn(8, 1024, seed=22) * 1e-3 + 5.0e3  # spread far below the mean
+    got = trident.function.var(y.to(device), 1, 1)
+    want = torch.var(y.double(), 1, correction=1)
+    assert torch.allclose(got.cpu().double(), want, rtol=1e-3, atol=0), (got.cpu().double() / want)

@@ -72,9 +72,12 @@ __global__ void __launch_bounds__(CTA_ROW ? 512 : 256)
       if (rt.tid == 0) out_a[row] = Traits<T>::from_f(KIND == RK_SUM ? s : s / n);
     } else {
       // Variance in one pass over the registers and one exchange: sums of d = x - c and of d^2 with
-      // the shift c = first element of the row (a sample of the row, so d is of the order of the
-      // spread and the subtraction below does not cancel): mean = c + S1/n, var = (S2 - S1^2/n)/(n-k).
-      const float shift = Traits<T>::to_f(__ldg(xr));
+      // the shift c = a sample of the row (so d is of the order of the spread and the subtraction
+      // below does not cancel): mean = c + S1/n, var = (S2 - S1^2/n)/(n-k).
+      // (the median of three samples, so that a single outlier cannot become the shift)
+      const float q0 = Traits<T>::to_f(__ldg(xr)), q1 = Traits<T>::to_f(__ldg(xr + cols / 2)),
+                  q2 = Traits<T>::to_f(__ldg(xr + cols - 1));
+      const float shift = fmaxf(fminf(q0, q1), fminf(fmaxf(q0, q1), q2));
       const uint64_t nshift2 = splat2(-shift);
       uint64_t s1 = 0ull, s2 = 0ull;
 #pragma unroll
