@@ -97,3 +97,16 @@ def test_half_precision_values(dt, atol, device):
     got = trident.function.layer_norm(x.to(device), (2048,), w.to(device), b.to(device))
     # one rounding of an fp32 result to the 16-bit type
     util.assert_half_close(got, want, dt, atol=1e-6, ulps=0.51, what="y")
+
+
+def test_large_mean_and_outlier(device):
+    """Mean and variance come from one pass of sums shifted by a sample of the row: a mean far from
+    zero and an outlier in the first position must not cost accuracy."""
+    x = util.randn(32, 1024, seed=31) * 0.5 + 200.0
+    x[:, 0] = 5.0e3
+    w, b = util.randn(1024, seed=32), util.randn(1024, seed=33)
+    want = torch.nn.functional.layer_norm(x.double(), (1024,), w.double(), b.double(), 1e-5)
+    got = trident.function.layer_norm(x.to(device), (1024,), w.to(device), b.to(device), 1e-5)
+    assert torch.allclose(got.cpu().double(), want, rtol=1e-4, atol=1e-4), (got.cpu().double() - want).abs().max()
+    ref32 = torch.nn.functional.layer_norm(x, (1024,), w, b, 1e-5)  # torch's own fp32 result as the yardstick
+    assert (got.cpu().double() - want).abs().max() <= 4 * (ref32.double() - want).abs().max() + 1e-5
