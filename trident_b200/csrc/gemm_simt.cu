@@ -121,14 +121,34 @@ __device__ inline float gelu_f(float g, bool tanh_form) {
   }
   return 0.5f * g * (1.f + erff(g * 0.7071067811865476f));
 }
-__device__ inline float gelu_grad_f(float g, bool tanh_form) {
+// GELU and its derivative together (the backward needs both, and they share their transcendentals).
+// For 16-bit tensors the erf form takes the normal CDF from one exponential and one reciprocal
+// (Abramowitz & Stegun 7.1.26, |error| <= 1.5e-7, far below the output's rounding step); the
+// exponential e^(-g*g/2) is the one the derivative needs. fp32 tensors use erff.
+template <typename T>
+__device__ inline void gelu_value_grad(float g, bool tanh_form, float& gel, float& grad) {
   if (tanh_form) {
     const float a = tanhf(0.7978845608028654f * g * (1.f + 0.044715f * g * g));
-    return 0.5f * (1.f + a + g * (1.f - a * a) * (0.7978845608028654f + 0.1070322244089f * g * g));
+    gel = 0.5f * g * (1.f + a);
+    grad = 0.5f * (1.f + a + g * (1.f - a * a) * (0.7978845608028654f + 0.1070322244089f * g * g));
+    return;
   }
-  const float cdf = 0.5f * (1.f + erff(g * 0.7071067811865476f));
-  const float pdf = 0.3989422804014327f * expf(-0.5f * g * g);
-  return cdf + g * pdf;
+  float cdf, pdf_e;
+  if constexpr (sizeof(T) == 2) {
+    const float t = __frcp_rn(fmaf(0.3275911f * 0.7071067811865476f, fabsf(g), 1.f));
+    pdf_e = exp2f(-0.7213475204444817f * g * g);
+    float poly = fmaf(t, 1.061405429f, -1.453152027f);
+    poly = fmaf(t, poly, 1.421413741f);
+    poly = fmaf(t, poly, -0.284496736f);
+    poly = fmaf(t, poly, 0.254829592f);
+    const float h = 0.5f * poly * t * pdf_e;  // the smaller tail
+    cdf = g < 0.f ? h : 1.f - h;
+  } else {
+    cdf = fmaf(0.5f, erff(g * 0.7071067811865476f), 0.5f);
+    pdf_e = __expf(-0.5f * g * g);
+  }
+  gel = g * cdf;
+  grad = fmaf(g * 0.3989422804014327f, pdf_e, cdf);
 }
 
 // out[r, j] = state * gelu(gate), from the already rounded state_gate [rows, 2X]
@@ -185,8 +205,10 @@ __global__ void geglu_bwd_elementwise_kernel(T* __restrict__ dsg, const T* __res
     float ds[V], dg[V];
 #pragma unroll
     for (int i = 0; i < V; ++i) {
-      ds[i] = dv[i] * gelu_f(gv[i], tanh_form);
-      dg[i] = dv[i] * sv[i] * gelu_grad_f(gv[i], tanh_form);
+      float gel, grad;
+      gelu_value_grad<T>(gv[i], tanh_form, gel, grad);
+      ds[i] = dv[i] * gel;
+      dg[i] = dv[i] * sv[i] * grad;
     }
     T* d = dsg + r * 2 * X + j;
     if constexpr (V > 1) {
@@ -216,25 +238,15 @@ __global__ void __launch_bounds__(256)
 #pragma unroll
   for (int i = 0; i < V; ++i) acc_s[i] = acc_g[i] = 0.f;
   if (j < X) {
-    for (int64_t r = r0 + threadIdx.y; r < r1; r += 8) {
-      const T* s = sg + r * 2 * X + j;
+    auto row_step = [&](int64_t r, const uint4& sraw, const uint4& graw, const uint4& draw) {
       float sv[V], gv[V], dv[V], ds[V], dg[V];
-      unpack<T>(ld_stream(s), sv);
-      unpack<T>(ld_stream(s + X), gv);
-      unpack<T>(ld_stream(dout + r * X + j), dv);
+      unpack<T>(sraw, sv);
+      unpack<T>(graw, gv);
+      unpack<T>(draw, dv);
 #pragma unroll
       for (int i = 0; i < V; ++i) {
-        const float g = gv[i];
         float gel, grad;
-        if (tanh_form) {
-          const float a = tanhf(0.7978845608028654f * g * (1.f + 0.044715f * g * g));
-          gel = 0.5f * g * (1.f + a);
-          grad = 0.5f * (1.f + a + g * (1.f - a * a) * (0.7978845608028654f + 0.1070322244089f * g * g));
-        } else {
-          const float cdf = fmaf(0.5f, erff(g * 0.7071067811865476f), 0.5f);
-          gel = g * cdf;
-          grad = fmaf(g * 0.3989422804014327f, __expf(-0.5f * g * g), cdf);
-        }
+        gelu_value_grad<T>(gv[i], tanh_form, gel, grad);
         ds[i] = dv[i] * gel;
         dg[i] = dv[i] * sv[i] * grad;
         acc_s[i] += ds[i];
@@ -243,6 +255,11 @@ __global__ void __launch_bounds__(256)
       T* d = dsg + r * 2 * X + j;
       st_stream(d, pack<T>(ds));
       st_stream(d + X, pack<T>(dg));
+    };
+    for (int64_t r = r0 + threadIdx.y; r < r1; r += 8) {
+      const T* s0 = sg + r * 2 * X + j;
+      const uint4 a0 = ld_stream(s0), a1 = ld_stream(s0 + X), a2 = ld_stream(dout + r * X + j);
+      row_step(r, a0, a1, a2);
     }
   }
 #pragma unroll
