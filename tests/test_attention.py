@@ -113,6 +113,34 @@ def test_half_forward_backward(B, H, S, D, is_causal, masked, dt, device):
         util.assert_half_close(g, w_, dt, atol=1e-2, ulps=1.0, what=name)
 
 
+@pytest.mark.parametrize("D", [64, 128])
+@pytest.mark.parametrize("mask_shape", ["bhss", "b1ss", "11ss", "b11s", "1h1s"])
+def test_half_mask_layouts(mask_shape, D, device):
+    """Every broadcast layout of an additive bf16 mask (finite values and -inf) on the tensor-core
+    kernels: full, broadcast over heads, over batch and heads, and over the query rows (a key
+    padding mask), four key tiles and two query-tile pairs long."""
+    dt = torch.bfloat16
+    B, H, S = 2, 3, 512
+    q, k, v, dy = (util.randn(B, H, S, D, seed=s, dtype=dt) for s in (1, 2, 3, 5))
+    shape = {"bhss": (B, H, S, S), "b1ss": (B, 1, S, S), "11ss": (1, 1, S, S), "b11s": (B, 1, 1, S),
+             "1h1s": (1, H, 1, S)}[mask_shape]
+    mask = util.randn(*shape, seed=4)
+    drop = util.rand(*shape, seed=6) < 0.2
+    drop[..., 0] = False
+    mask = mask.masked_fill(drop, float("-inf")).to(dt)
+
+    def train(fn, dev, up):
+        i, j, l = (t.detach().clone().to(dev).to(up).requires_grad_(True) for t in (q, k, v))
+        y = fn(i, j, l, attn_mask=mask.to(dev).to(up))
+        y.backward(dy.to(dev).to(up))
+        return y, i.grad, j.grad, l.grad
+
+    got = train(trident.function.scaled_dot_product_attention, device, dt)
+    want = train(torch_oracle.scaled_dot_product_attention, "cpu", torch.float32)
+    for g, w_, name in zip(got, want, ["y", "dq", "dk", "dv"]):
+        util.assert_half_close(g, w_, dt, atol=1e-2, ulps=1.0, what=f"{mask_shape} D={D} {name}")
+
+
 def test_argument_errors(device):
     f = trident.function.scaled_dot_product_attention
     q = torch.randn(1, 1, 8, 16, device=device)

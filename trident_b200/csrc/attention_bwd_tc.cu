@@ -748,13 +748,16 @@ int launch_attn_bwd_tc(void* dq, void* dk, void* dv, const void* dout, const voi
   p.mask_tma = 0;
   p.mask_has_b = mask && a.ms[0] != 0;
   p.mask_has_h = mask && a.ms[1] != 0;
-  if (mask && a.D == 64 && a.ms[3] == 1 && aligned16(mask) && a.ms[2] % 8 == 0 &&
-      (!p.mask_has_h || a.ms[1] % 8 == 0) && (!p.mask_has_b || a.ms[0] % 8 == 0)) {
+  if (mask && a.D == 64 && a.ms[3] == 1 && aligned16(mask) && a.ms[2] > 0 && a.ms[2] % 8 == 0 &&
+      (!p.mask_has_h || (a.ms[1] > 0 && a.ms[1] % 8 == 0)) && (!p.mask_has_b || (a.ms[0] > 0 && a.ms[0] % 8 == 0))) {
     // the mask seen as [Bm, Hm, S(query), S(key)] with its broadcast dimensions collapsed to 1
+    // (a mask broadcast over the query rows, or one the driver refuses a tensor map for, is read
+    // with plain loads instead)
     const int64_t mst[4] = {a.ms[0], a.ms[1], a.ms[2], 1};
-    if (!make_tensor_map_bhsd(&mmask, mask, p.mask_has_b ? a.B : 1, p.mask_has_h ? a.H : 1, a.S, a.S, mst, 128))
-      return TB200_ERR_UNSUPPORTED;
-    p.mask_tma = 1;
+    if (make_tensor_map_bhsd(&mmask, mask, p.mask_has_b ? a.B : 1, p.mask_has_h ? a.H : 1, a.S, a.S, mst, 128))
+      p.mask_tma = 1;
+    else
+      mmask = mq;
   }
   p.a = a;
   p.dk = dk;

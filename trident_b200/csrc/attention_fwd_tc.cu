@@ -62,6 +62,8 @@ struct FwdParams {
   float* lse;
   const void* mask;
   int mask_vec;       // mask rows can be read with 16-byte loads
+  int mask_tma;       // the [128 q][128 kv] mask tiles are staged in shared memory by bulk tensor copies
+  int mask_has_b, mask_has_h;  // 0 when that mask dimension is broadcast
   int* status;
   float scale_log2;   // softmax scale * log2(e)
   int nq;             // query tiles per (batch, head)
@@ -120,8 +122,14 @@ __device__ long long g_prof_fwd[64];
 template <typename T, int D, bool CAUSAL, bool MASKED>
 __global__ void __launch_bounds__(FWD_THREADS, 1)
     attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
-                       const __grid_constant__ CUtensorMap map_v, const FwdParams p) {
+                       const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_mask,
+                       const FwdParams p) {
   constexpr int TILE_BYTES = 128 * D * 2;
+  // At D = 64 there is shared memory left for one [128 q][128 kv] mask tile per query tile: a
+  // thread's row segment then comes from shared memory (conflict-free 16-byte reads of the
+  // 128-byte swizzled boxes) instead of 16 global loads that each touch 32 different lines per warp.
+  constexpr bool MASK_SMEM = MASKED && D == 64;
+  constexpr int MASK_TILE_BYTES = 128 * 128 * 2;
   constexpr int NBOX = D / 64;
   constexpr int BOX_BYTES = 128 * 64 * 2;
   constexpr bool IS_BF16 = std::is_same<T, __nv_bfloat16>::value;
@@ -135,7 +143,8 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
   uint8_t* q_smem = smem;                       // [2][TILE_BYTES]
   uint8_t* k_smem = smem + 2 * TILE_BYTES;      // [2][TILE_BYTES]
   uint8_t* v_smem = smem + 4 * TILE_BYTES;      // [2][TILE_BYTES]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 6 * TILE_BYTES);
+  uint8_t* mask_smem = smem + 6 * TILE_BYTES;   // [2][MASK_TILE_BYTES] when MASK_SMEM
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 6 * TILE_BYTES + (MASK_SMEM ? 2 * MASK_TILE_BYTES : 0));
   uint64_t* q_full = bars;         // [2]
   uint64_t* k_full = bars + 2;     // [2]
   uint64_t* k_empty = bars + 4;    // [2]
@@ -144,7 +153,9 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
   uint64_t* s_full = bars + 10;    // [2]  MMA -> softmax: scores ready
   uint64_t* p_full = bars + 12;    // [2]  softmax -> MMA: probabilities written
   uint64_t* o_done = bars + 14;    // [2]  MMA -> softmax: P V accumulated
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
+  uint64_t* mask_full = bars + 16;   // [2]  mask producer -> softmax of query tile t
+  uint64_t* mask_empty = bars + 18;  // [2]  softmax -> mask producer: tile copied to registers
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 20);
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -173,11 +184,16 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
     ptx::mbar_init(&p_full[1], 128);
     ptx::mbar_init(&o_done[0], 1);
     ptx::mbar_init(&o_done[1], 1);
+    ptx::mbar_init(&mask_full[0], 1);
+    ptx::mbar_init(&mask_full[1], 1);
+    ptx::mbar_init(&mask_empty[0], 128);
+    ptx::mbar_init(&mask_empty[1], 128);
     *abort_flag = 0;
     ptx::fence_barrier_init();
     ptx::prefetch_tensormap(&map_q);
     ptx::prefetch_tensormap(&map_k);
     ptx::prefetch_tensormap(&map_v);
+    if (MASK_SMEM && p.mask_tma) ptx::prefetch_tensormap(&map_mask);
   }
   if (warp == 2) {
     ptx::tmem_alloc(tmem_slot, TMEM_COLS);
@@ -222,6 +238,26 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
 #pragma unroll
       for (int c = 0; c < NBOX; ++c)
         tma_load_4d(v_smem + st * TILE_BYTES + c * BOX_BYTES, &map_v, &v_full[st], c * 64, j * TK, h, b);
+    }
+  } else if (MASK_SMEM && warp == 3 && lane == 0) {
+    // ---------------------------------------------------------------- mask producer
+    // One buffer per query tile: the softmax threads copy their row segment to registers as
+    // soon as the tile has landed and hand the buffer back, so the next tile's copy is in
+    // flight while they work on the scores of the current one.
+    if (p.mask_tma) {
+      for (int j = 0; j < nmax; ++j) {
+#pragma unroll
+        for (int t = 0; t < 2; ++t) {
+          if (j < (t == 0 ? n0 : n1)) {
+            ptx::mbar_wait(&mask_empty[t], (j & 1) ^ 1, abort_flag, p.status, 13 + t);
+            ptx::mbar_expect_tx(&mask_full[t], MASK_TILE_BYTES);
+#pragma unroll
+            for (int c = 0; c < 2; ++c)
+              tma_load_4d(mask_smem + t * MASK_TILE_BYTES + c * BOX_BYTES, &map_mask, &mask_full[t], j * TK + c * 64,
+                          (t == 0 ? qt0 : qt1) * TQ, p.mask_has_h ? h : 0, p.mask_has_b ? b : 0);
+          }
+        }
+      }
     }
   } else if (warp == 1 && lane == 0) {
     // ---------------------------------------------------------------- MMA issuer
@@ -326,13 +362,30 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
       // for, so their latency hides behind the QK^T product (16-byte loads, kept packed)
       uint4 mraw[MASKED ? 16 : 1];
       if constexpr (MASKED) {
-        if (p.mask_vec) {
+        if (MASK_SMEM && p.mask_tma) {
+          ptx::mbar_wait(&mask_full[t], j & 1, abort_flag, p.status, 30);
+          // 16-byte chunk c of row r sits at r * 128 + ((c ^ (r & 7)) << 4) of its [128][64] box
+          const uint32_t row_addr = ptx::smem_u32(mask_smem + t * MASK_TILE_BYTES) + row_in_tile * 128;
+#pragma unroll
+          for (int c = 0; c < 16; ++c) {
+            const uint32_t addr = row_addr + (c >> 3) * BOX_BYTES + (((c & 7) ^ (row_in_tile & 7)) << 4);
+            asm volatile("ld.volatile.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
+                         : "=r"(mraw[c].x), "=r"(mraw[c].y), "=r"(mraw[c].z), "=r"(mraw[c].w)
+                         : "r"(addr)
+                         : "memory");
+          }
+          // The buffer is handed back before any loaded value is used: the fence makes the loads
+          // complete first (without it the next tile's copy was seen overwriting rows that had
+          // not been read yet).
+          asm volatile("fence.acq_rel.cta;" ::: "memory");
+          ptx::mbar_arrive(&mask_empty[t]);
+        } else if (p.mask_vec) {
 #pragma unroll
           for (int c = 0; c < 16; ++c) mraw[c] = __ldg(reinterpret_cast<const uint4*>(mask_row + kv0 + c * 8));
         }
       }
       auto mask32 = [&](float (&mv)[32], int c) {
-        if (p.mask_vec) {
+        if (p.mask_vec) {  // (implied by mask_tma)
 #pragma unroll
           for (int jv = 0; jv < 4; ++jv) {
             float f[8];
@@ -578,9 +631,9 @@ bool attn_tc_supported(const AttnArgs& a, int dtype, const void* q, const void* 
 }
 
 template <typename T, int D, bool CAUSAL, bool MASKED>
-static int launch_fwd(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const FwdParams& p,
-                      cudaStream_t st) {
-  constexpr int SMEM = 6 * 128 * D * 2 + 1024 + 256;
+static int launch_fwd(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& mmask,
+                      const FwdParams& p, cudaStream_t st) {
+  constexpr int SMEM = 6 * 128 * D * 2 + ((MASKED && D == 64) ? 2 * 128 * 128 * 2 : 0) + 1024 + 256;
   auto kern = attn_fwd_tc_kernel<T, D, CAUSAL, MASKED>;
   static std::once_flag once;
   static cudaError_t attr_err = cudaSuccess;
@@ -602,7 +655,7 @@ static int launch_fwd(const CUtensorMap& mq, const CUtensorMap& mk, const CUtens
     return TB200_ERR_UNSUPPORTED;
   }
   dim3 grid((unsigned)((p.nq + 1) / 2), (unsigned)(p.a.B * p.a.H));
-  kern<<<grid, FWD_THREADS, SMEM, st>>>(mq, mk, mv, p);
+  kern<<<grid, FWD_THREADS, SMEM, st>>>(mq, mk, mv, mmask, p);
   return launch_status("attn_fwd_tc");
 }
 
@@ -622,12 +675,27 @@ int launch_attn_fwd_tc(void* out, float* lse, const void* q, const void* k, cons
   p.status = device_status_ptr();
   p.scale_log2 = a.scale * LOG2E;
   p.nq = (int)(a.S / TQ);
+  CUtensorMap mmask = mq;  // placeholder when no mask tile is staged
+  p.mask_tma = 0;
+  p.mask_has_b = mask && a.ms[0] != 0;
+  p.mask_has_h = mask && a.ms[1] != 0;
+  if (mask && !a.causal && a.D == 64 && p.mask_vec && a.ms[2] > 0 && (!p.mask_has_h || a.ms[1] > 0) &&
+      (!p.mask_has_b || a.ms[0] > 0)) {
+    // the mask seen as [Bm, Hm, S(query), S(key)] with its broadcast dimensions collapsed to 1
+    // (a mask broadcast over the query rows, or one the driver refuses a tensor map for, is read
+    // with plain loads instead)
+    const int64_t mst[4] = {a.ms[0], a.ms[1], a.ms[2], 1};
+    if (make_tensor_map_bhsd(&mmask, mask, p.mask_has_b ? a.B : 1, p.mask_has_h ? a.H : 1, a.S, a.S, mst, 128))
+      p.mask_tma = 1;
+    else
+      mmask = mq;
+  }
   auto go = [&](auto tag, auto dsel) -> int {
     using T = decltype(tag);
     constexpr int D = decltype(dsel)::value;
-    if (a.causal) return launch_fwd<T, D, true, false>(mq, mk, mv, p, st);
-    if (mask) return launch_fwd<T, D, false, true>(mq, mk, mv, p, st);
-    return launch_fwd<T, D, false, false>(mq, mk, mv, p, st);
+    if (a.causal) return launch_fwd<T, D, true, false>(mq, mk, mv, mmask, p, st);
+    if (mask) return launch_fwd<T, D, false, true>(mq, mk, mv, mmask, p, st);
+    return launch_fwd<T, D, false, false>(mq, mk, mv, mmask, p, st);
   };
   if (dtype == TB200_BF16)
     return a.D == 128 ? go(__nv_bfloat16{}, IntD<128>{}) : go(__nv_bfloat16{}, IntD<64>{});
