@@ -43,7 +43,7 @@ constexpr int FWD_THREADS = 384;
 // Register allowances of the kernel's warps (see the setmaxnreg calls): the kernel must be launched
 // with REGS_LAUNCH registers per thread for the totals to fit the CTA's pool; the host checks the
 // compiled kernel's register count before the first launch.
-constexpr int REGS_LAUNCH = 168, REGS_SERVICE = 48, REGS_SOFTMAX = 224;
+constexpr int REGS_LAUNCH = 168, REGS_SERVICE = 56, REGS_SOFTMAX = 224;
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr float LN2 = 0.6931471805599453f;
 constexpr float RESCALE_THRESHOLD = 8.f;
@@ -259,37 +259,48 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
         }
       }
     }
-  } else if (warp == 1 && lane == 0) {
+  } else if (warp == 1) {
     // ---------------------------------------------------------------- MMA issuer
+    // The whole warp walks the loop; one elected lane waits, issues and commits.
+    const bool elected = ptx::elect_one();
+    auto wait_ = [&](uint64_t* bar, uint32_t parity, int code) {
+      if (elected) ptx::mbar_wait(bar, parity, abort_flag, p.status, code);
+      __syncwarp();
+    };
+    auto commit_ = [&](uint64_t* bar) {
+      if (elected) ptx::umma_commit(bar);
+    };
     auto issue_qk = [&](int t, int st) {
       const uint32_t qa = ptx::smem_u32(q_smem + t * TILE_BYTES);
       const uint32_t ka = ptx::smem_u32(k_smem + st * TILE_BYTES);
 #pragma unroll
       for (int ks = 0; ks < D / 16; ++ks) {
         const uint32_t off = (ks >> 2) * BOX_BYTES + (ks & 3) * 32;
-        ptx::umma_ss(tmem_base + COL_S + t * 128, ptx::make_smem_desc(qa + off, 16, 1024),
-                     ptx::make_smem_desc(ka + off, 16, 1024), IDESC_QK, ks != 0);
+        if (elected)
+          ptx::umma_ss(tmem_base + COL_S + t * 128, ptx::make_smem_desc(qa + off, 16, 1024),
+                       ptx::make_smem_desc(ka + off, 16, 1024), IDESC_QK, ks != 0);
       }
     };
     auto issue_pv = [&](int t, int st, bool accumulate) {
       const uint32_t va = ptx::smem_u32(v_smem + st * TILE_BYTES);
 #pragma unroll
       for (int ks = 0; ks < TK / 16; ++ks) {
-        ptx::umma_ts(tmem_base + COL_O + t * D, tmem_base + COL_S + t * 128 + ks * 8,
-                     ptx::make_smem_desc(va + ks * 2048, BOX_BYTES, 1024), IDESC_PV, accumulate || ks != 0);
+        if (elected)
+          ptx::umma_ts(tmem_base + COL_O + t * D, tmem_base + COL_S + t * 128 + ks * 8,
+                       ptx::make_smem_desc(va + ks * 2048, BOX_BYTES, 1024), IDESC_PV, accumulate || ks != 0);
       }
     };
-    ptx::mbar_wait(&q_full[0], 0, abort_flag, p.status, 21);
-    if (active1) ptx::mbar_wait(&q_full[1], 0, abort_flag, p.status, 22);
-    ptx::mbar_wait(&k_full[0], 0, abort_flag, p.status, 23);
+    wait_(&q_full[0], 0, 21);
+    if (active1) wait_(&q_full[1], 0, 22);
+    wait_(&k_full[0], 0, 23);
     ptx::tc_fence_after();
     issue_qk(0, 0);
-    ptx::umma_commit(&s_full[0]);
+    commit_(&s_full[0]);
     if (n1 > 0) {
       issue_qk(1, 0);
-      ptx::umma_commit(&s_full[1]);
+      commit_(&s_full[1]);
     }
-    ptx::umma_commit(&k_empty[0]);
+    commit_(&k_empty[0]);
     PROF_DECL
     for (int j = 0; j < nmax; ++j) {
       const int st = j & 1, nst = (j + 1) & 1;
@@ -298,45 +309,45 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
       bool k_next_ready = false;
       if (j < n0) {
         PROF(0);
-        ptx::mbar_wait(&p_full[0], jp, abort_flag, p.status, 24);
+        wait_(&p_full[0], jp, 24);
         PROF(1);
-        ptx::mbar_wait(&v_full[st], ph, abort_flag, p.status, 25);
+        wait_(&v_full[st], ph, 25);
         PROF(2);
         ptx::tc_fence_after();
         issue_pv(0, st, j > 0);
-        ptx::umma_commit(&o_done[0]);
-        if (j >= n1) ptx::umma_commit(&v_empty[st]);
+        commit_(&o_done[0]);
+        if (j >= n1) commit_(&v_empty[st]);
       }
       if (j + 1 < n0) {
         PROF(3);
-        ptx::mbar_wait(&k_full[nst], nph, abort_flag, p.status, 26);
+        wait_(&k_full[nst], nph, 26);
         PROF(4);
         k_next_ready = true;
         ptx::tc_fence_after();
         issue_qk(0, nst);
-        ptx::umma_commit(&s_full[0]);
-        if (j + 1 >= n1) ptx::umma_commit(&k_empty[nst]);
+        commit_(&s_full[0]);
+        if (j + 1 >= n1) commit_(&k_empty[nst]);
       }
       if (j < n1) {
         PROF(5);
-        ptx::mbar_wait(&p_full[1], jp, abort_flag, p.status, 27);
+        wait_(&p_full[1], jp, 27);
         PROF(6);
-        ptx::mbar_wait(&v_full[st], ph, abort_flag, p.status, 28);
+        wait_(&v_full[st], ph, 28);
         ptx::tc_fence_after();
         issue_pv(1, st, j > 0);
-        ptx::umma_commit(&o_done[1]);
-        ptx::umma_commit(&v_empty[st]);
+        commit_(&o_done[1]);
+        commit_(&v_empty[st]);
       }
       if (j + 1 < n1) {
-        if (!k_next_ready) ptx::mbar_wait(&k_full[nst], nph, abort_flag, p.status, 29);
+        if (!k_next_ready) wait_(&k_full[nst], nph, 29);
         ptx::tc_fence_after();
         issue_qk(1, nst);
-        ptx::umma_commit(&s_full[1]);
-        ptx::umma_commit(&k_empty[nst]);
+        commit_(&s_full[1]);
+        commit_(&k_empty[nst]);
       }
       PROF(7);
     }
-    PROF_FLUSH(0);
+    if (elected) PROF_FLUSH(0);
   }
   } else {
     // ---------------------------------------------------------------- softmax + epilogue
