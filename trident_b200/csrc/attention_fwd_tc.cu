@@ -137,6 +137,11 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
   constexpr uint32_t IDESC_PV = ptx::make_idesc(IS_BF16, false, true, TQ, D);
   constexpr uint32_t TMEM_COLS = 512;
   constexpr uint32_t COL_S = 0, COL_O = 256;
+  // At D = 64 the output accumulators leave 128 columns free: P gets columns of its own instead of
+  // overwriting S, so the next score product of a query tile is issued as soon as the softmax
+  // threads hold the current scores in registers (it no longer has to follow the P V product).
+  constexpr bool P_SPLIT = D == 64;
+  constexpr uint32_t COL_P = 384;
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -155,7 +160,8 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
   uint64_t* o_done = bars + 14;    // [2]  MMA -> softmax: P V accumulated
   uint64_t* mask_full = bars + 16;   // [2]  mask producer -> softmax of query tile t
   uint64_t* mask_empty = bars + 18;  // [2]  softmax -> mask producer: tile copied to registers
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 20);
+  uint64_t* s_free = bars + 20;      // [2]  softmax -> MMA: scores read into registers (P_SPLIT)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 22);
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -188,6 +194,8 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
     ptx::mbar_init(&mask_full[1], 1);
     ptx::mbar_init(&mask_empty[0], 128);
     ptx::mbar_init(&mask_empty[1], 128);
+    ptx::mbar_init(&s_free[0], 128);
+    ptx::mbar_init(&s_free[1], 128);
     *abort_flag = 0;
     ptx::fence_barrier_init();
     ptx::prefetch_tensormap(&map_q);
@@ -286,7 +294,7 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
 #pragma unroll
       for (int ks = 0; ks < TK / 16; ++ks) {
         if (elected)
-          ptx::umma_ts(tmem_base + COL_O + t * D, tmem_base + COL_S + t * 128 + ks * 8,
+          ptx::umma_ts(tmem_base + COL_O + t * D, tmem_base + (P_SPLIT ? COL_P + t * 64 : COL_S + t * 128) + ks * 8,
                        ptx::make_smem_desc(va + ks * 2048, BOX_BYTES, 1024), IDESC_PV, accumulate || ks != 0);
       }
     };
@@ -302,6 +310,37 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
     }
     commit_(&k_empty[0]);
     PROF_DECL
+    if constexpr (P_SPLIT) {
+      for (int j = 0; j < nmax; ++j) {
+        const int st = j & 1, nst = (j + 1) & 1;
+        const uint32_t ph = (j >> 1) & 1, nph = ((j + 1) >> 1) & 1;
+        const uint32_t jp = j & 1;
+        bool k_next_ready = false;
+#pragma unroll
+        for (int t = 0; t < 2; ++t) {
+          const int nt = t == 0 ? n0 : n1, no = t == 0 ? n1 : n0;
+          // the last user of a K or V stage releases it: tile 1 when it takes part, else tile 0
+          const bool last_k = t == 1 || j + 1 >= no, last_v = t == 1 || j >= no;
+          if (j + 1 < nt) {
+            wait_(&s_free[t], jp, 35 + t);
+            if (!k_next_ready) wait_(&k_full[nst], nph, 26);
+            k_next_ready = true;
+            ptx::tc_fence_after();
+            issue_qk(t, nst);
+            commit_(&s_full[t]);
+            if (last_k) commit_(&k_empty[nst]);
+          }
+          if (j < nt) {
+            wait_(&p_full[t], jp, 24 + 3 * t);
+            wait_(&v_full[st], ph, 25 + 3 * t);
+            ptx::tc_fence_after();
+            issue_pv(t, st, j > 0);
+            commit_(&o_done[t]);
+            if (last_v) commit_(&v_empty[st]);
+          }
+        }
+      }
+    } else {
     for (int j = 0; j < nmax; ++j) {
       const int st = j & 1, nst = (j + 1) & 1;
       const uint32_t ph = (j >> 1) & 1, nph = ((j + 1) >> 1) & 1;
@@ -347,6 +386,7 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
       }
       PROF(7);
     }
+    }
     if (elected) PROF_FLUSH(0);
   }
   } else {
@@ -361,6 +401,7 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
     const uint32_t lane_off = static_cast<uint32_t>(quarter * 32) << 16;
     const uint32_t s_addr = tmem_base + lane_off + COL_S + t * 128;
     const uint32_t o_addr = tmem_base + lane_off + COL_O + t * D;
+    const uint32_t p_addr = tmem_base + lane_off + (P_SPLIT ? COL_P + t * 64 : COL_S + t * 128);
     const T* mask_row = nullptr;
     if constexpr (MASKED)
       mask_row = reinterpret_cast<const T*>(p.mask) + (long long)b * p.a.ms[0] + (long long)h * p.a.ms[1] +
@@ -472,6 +513,11 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
         scale32(sr[3], 3);
       }
       PROF(2);
+      if constexpr (P_SPLIT) {
+        // the scores are in registers: the score columns may take the next product
+        ptx::tc_fence_before();
+        ptx::mbar_arrive(&s_free[t]);
+      }
       const float m_new = fmaxf(m_used, mx);
       if (j == 0) {
         m_used = m_new;
@@ -498,7 +544,7 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
       }
       const float m_safe = m_used == -INFINITY ? 0.f : m_used;
       PROF(3);
-      // pass 2: probabilities, row sum, P written over S as packed 16-bit pairs
+      // pass 2: probabilities, row sum, P written as packed 16-bit pairs (over S, or to its own columns)
       {
         const uint64_t scale2 = plain ? am::pack2f(p.scale_log2, p.scale_log2) : am::pack2f(1.f, 1.f);
         const uint64_t negm2 = am::pack2f(-m_safe, -m_safe);
@@ -520,8 +566,16 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
             lsum = am::add2(lsum, am::pack2f(p0, p1));
             packed[i >> 1] = am::cvt_pair<T>(p0, p1);
           }
-          ptx::tmem_st16(s_addr + c * 16, packed);
+          ptx::tmem_st16(p_addr + c * 16, packed);
         };
+        if constexpr (P_SPLIT) {
+          // P(j) goes over P(j-1): the product that read it must have completed (it has, as a rule:
+          // it was issued a whole pass ago)
+          if (j > 0) {
+            ptx::mbar_wait(&o_done[t], (j - 1) & 1, abort_flag, p.status, 34);
+            ptx::tc_fence_after();
+          }
+        }
         exp32(sr[0], 0);
         exp32(sr[1], 1);
         exp32(sr[2], 2);
