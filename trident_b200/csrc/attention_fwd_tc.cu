@@ -7,15 +7,21 @@
 // so that the tensor pipe works on one query tile while the softmax warps work on the other:
 //
 //   warp 0      TMA producer: Q0, Q1 once, then a 2-stage ring of K tiles and one of V tiles
-//   warp 1      MMA issuer (one thread):  S_t = Q_t K_j^T  (both operands K-major in smem),
+//   warp 1      MMA issuer (the warp walks the loop, one elected lane issues):
+//               S_t = Q_t K_j^T  (both operands K-major in smem),
 //               O_t += P_t V_j (P_t read from tensor memory, V_j MN-major in smem)
 //   warp 2      tensor-memory allocation
+//   warp 3      at D = 64 with a mask: producer of the [128 q][128 kv] mask tiles (one shared-memory
+//               buffer per query tile; the softmax threads copy their row segment to registers,
+//               fence, and hand the buffer back)
 //   warps 4-7   softmax of query tile 0, warps 8-11 of query tile 1: one thread per score
 //               row; row maximum and sum need no shuffles. The 128 scores of the row are read
 //               from tensor memory once and stay in registers between the maximum and the
 //               exponentials (the softmax warps raise their register allowance with setmaxnreg,
 //               the four service warps lower theirs). exp2 with the softmax scale and log2(e)
-//               folded in; P is written back over S as packed 16-bit values.
+//               folded in; P is written back as packed 16-bit values: over S at D = 128 (tensor
+//               memory is full), to columns of its own at D = 64, where the next score product of
+//               the tile is issued as soon as the scores are in registers instead of after P V.
 //
 // The running maximum used for the exponent is only advanced when the true maximum has
 // moved by more than 8 (in log2 units); only then is the accumulator O_t rescaled in tensor
