@@ -97,6 +97,21 @@ __device__ inline void tma_load_4d(void* smem_dst, const CUtensorMap* map, uint6
       : "memory");
 }
 
+// Eight 16-bit values as four fp32 pairs (for the two-lane fp32 instructions).
+template <typename T>
+__device__ inline void pairs8(const uint4& raw, uint64_t (&out)[4]) {
+  const uint32_t* w = reinterpret_cast<const uint32_t*>(&raw);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    if constexpr (std::is_same<T, __nv_bfloat16>::value) {
+      out[i] = am::pack2u(w[i] << 16, w[i] & 0xffff0000u);
+    } else {
+      const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+      out[i] = am::pack2f(f.x, f.y);
+    }
+  }
+}
+
 // 32 additive-mask values of one row, pre-multiplied by log2(e).
 template <typename T>
 __device__ inline void load_mask32(float (&mv)[32], const T* row, long long col, long long stride, bool vec) {
@@ -494,6 +509,32 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
       } else {
         const int lim = CAUSAL ? row_in_tile : 1 << 30;  // columns above `lim` are masked (diagonal tile)
         auto scale32 = [&](uint32_t (&r)[32], int c) {
+          if constexpr (MASKED && !CAUSAL) {
+            if (p.mask_vec) {
+              // packed path: score * scale + mask * log2(e) on fp32 pairs, two values per maximum
+              const uint64_t scale2 = am::pack2f(p.scale_log2, p.scale_log2), log2e2 = am::pack2f(LOG2E, LOG2E);
+              float mx1 = -INFINITY;
+#pragma unroll
+              for (int jv = 0; jv < 4; ++jv) {
+                uint64_t m2[4];
+                pairs8<T>(mraw[MASKED ? c * 4 + jv : 0], m2);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                  const int idx = jv * 8 + i * 2;
+                  const uint64_t sc =
+                      am::fma2(am::pack2u(r[idx], r[idx + 1]), scale2, am::mul2(m2[i], log2e2));
+                  float a, b;
+                  am::unpack2f(sc, a, b);
+                  if (i & 1) mx1 = am::max3(mx1, a, b);
+                  else mx = am::max3(mx, a, b);
+                  r[idx] = __float_as_uint(a);
+                  r[idx + 1] = __float_as_uint(b);
+                }
+              }
+              mx = fmaxf(mx, mx1);
+              return;
+            }
+          }
           float mv[32];
           if constexpr (MASKED) mask32(mv, c);
 #pragma unroll
