@@ -30,6 +30,12 @@ FWD_PHASES = {
     2: ("softmax warps, tile 1", ["loop top", "wait S", "load S + maximum", "rescale check", "exp2 + store P",
                                   "store wait + arrive"]),
 }
+# At D = 64 the issuer's loop is ordered differently (P has columns of its own, the next score
+# product of a tile is issued before its P V product).
+FWD_PHASES_D64 = dict(FWD_PHASES)
+FWD_PHASES_D64[0] = ("MMA issuer", ["issue P.V(tile 1) + loop top", "wait S free(tile 0) + K(next)",
+                                    "issue Q.K^T(tile 0, next)", "wait P(tile 0) + V", "issue P.V(tile 0)",
+                                    "wait S free(tile 1)", "issue Q.K^T(tile 1, next)", "wait P(tile 1)"])
 BWD_PHASES = {
     0: ("MMA issuer", ["wait dQ drained", "issue dP^T", "wait P^T", "issue dV", "wait Q/dO(next)", "issue S^T(next)",
                        "wait dS^T", "issue dK, dQ"]),
@@ -103,7 +109,7 @@ def run(B=1, H=8, S=4096, D=128, causal=True, masked=False):
     tiles = S // 128  # CTA (0, 0) owns the longest row of tiles in both kernels
     lib.tb200_debug_read_prof_fwd(buf)
     _table(f"forward, q,k,v [{B},{H},{S},{D}] bf16, causal={causal}, masked={masked}: CTA (0,0), {tiles} key tiles",
-           buf, FWD_PHASES, tiles)
+           buf, FWD_PHASES_D64 if D == 64 else FWD_PHASES, tiles)
     lib.tb200_debug_read_prof(buf)
     _table(f"backward, same inputs: CTA (0,0), {tiles} query tiles", buf, BWD_PHASES, tiles)
     print("device status", _lib.device_status(False))

@@ -343,17 +343,21 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
           // the last user of a K or V stage releases it: tile 1 when it takes part, else tile 0
           const bool last_k = t == 1 || j + 1 >= no, last_v = t == 1 || j >= no;
           if (j + 1 < nt) {
+            PROF(t * 4 + 0);
             wait_(&s_free[t], jp, 35 + t);
             if (!k_next_ready) wait_(&k_full[nst], nph, 26);
             k_next_ready = true;
+            PROF(t * 4 + 1);
             ptx::tc_fence_after();
             issue_qk(t, nst);
             commit_(&s_full[t]);
             if (last_k) commit_(&k_empty[nst]);
           }
           if (j < nt) {
+            PROF(t * 4 + 2);
             wait_(&p_full[t], jp, 24 + 3 * t);
             wait_(&v_full[st], ph, 25 + 3 * t);
+            PROF(t * 4 + 3);
             ptx::tc_fence_after();
             issue_pv(t, st, j > 0);
             commit_(&o_done[t]);
