@@ -141,6 +141,25 @@ def test_half_mask_layouts(mask_shape, D, device):
         util.assert_half_close(g, w_, dt, atol=1e-2, ulps=1.0, what=f"{mask_shape} D={D} {name}")
 
 
+@pytest.mark.parametrize("D", [64, 128])
+def test_masked_forward_is_repeatable(D, device):
+    """The masked forward gives the same bits on every run (the shared-memory mask buffer of the
+    D = 64 kernel is handed back to its producer only after the row segments have been read)."""
+    dt = torch.bfloat16
+    B, H, S = 1, 4, 1024
+    q, k, v = (util.randn(B, H, S, D, seed=s, dtype=dt).to(device) for s in (1, 2, 3))
+    drop = util.rand(B, 1, S, S, seed=6) < 0.1
+    drop[..., 0] = False
+    mask = torch.zeros(B, 1, S, S).masked_fill(drop, float("-inf")).to(dt).to(device)
+    first = trident.function.scaled_dot_product_attention(q, k, v, attn_mask=mask)
+    want = torch_oracle.scaled_dot_product_attention(q.float().cpu(), k.float().cpu(), v.float().cpu(),
+                                                      attn_mask=mask.float().cpu())
+    util.assert_half_close(first, want, dt, atol=1e-2, ulps=1.0, what="y")
+    for _ in range(20):
+        again = trident.function.scaled_dot_product_attention(q, k, v, attn_mask=mask)
+        assert torch.equal(first, again)
+
+
 def test_argument_errors(device):
     f = trident.function.scaled_dot_product_attention
     q = torch.randn(1, 1, 8, 16, device=device)
