@@ -86,6 +86,9 @@ def test_broadcast_mask(mask_shape, device):
         (2, 1, 256, 64, False, True),
         (1, 1, 1024, 128, True, False),
         (1, 2, 384 + 128, 64, True, False),
+        (1, 2, 128, 64, False, True),
+        (1, 1, 128, 64, True, False),
+        (1, 2, 384 + 128, 64, False, True),
     ],
 )
 def test_half_forward_backward(B, H, S, D, is_causal, masked, dt, device):
