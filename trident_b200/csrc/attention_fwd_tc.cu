@@ -455,6 +455,7 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
           // complete first (without it the next tile's copy was seen overwriting rows that had
           // not been read yet).
           asm volatile("fence.acq_rel.cta;" ::: "memory");
+          ptx::fence_proxy_async_smem();  // the buffer's next writer is the async proxy (bulk tensor copy)
           ptx::mbar_arrive(&mask_empty[t]);
         } else if (p.mask_vec) {
 #pragma unroll
