@@ -476,7 +476,7 @@ def run_reference(args, wl):
 
 
 def measure(wl, args, rank, world, device, with_cpu, sampler=None):
-    from trident_b200.workloads import set_replica
+    from workloads import set_replica
 
     pk = peaks()
     kw = {"scale": args.scale} if args.scale > 1 else {}
@@ -555,7 +555,7 @@ def main():
                                    f"--nproc-per-node={args.gpus}", "--master-addr", "127.0.0.1",
                                    "--master-port", os.environ.get("MASTER_PORT", "29533"), __file__] + sys.argv[1:])
 
-    from trident_b200.workloads import WORKLOADS
+    from workloads import WORKLOADS
 
     wl = WORKLOADS[args.workload]
     if args.impl == "reference":

@@ -72,7 +72,10 @@ int tb200_layer_norm_bwd(void* dx, void* dweight /*nullable*/, void* dbias /*nul
  *   - all calls on one device share the array: two calls that may run on the GPU at the
  *     same time (different streams) race on it and must be serialised by the caller.
  *     Nothing in the array has to be cleared between calls; each call overwrites every
- *     element it later reads. */
+ *     element it later reads;
+ *   - the resolved address is remembered per device ordinal for the life of the process: a
+ *     process that calls cudaDeviceReset and then uses this entry point again on the same
+ *     device would be handed the address of the destroyed context. */
 int tb200_layer_norm_bwd_static(void* dx, void* dweight /*nullable*/, void* dbias /*nullable*/,
                                 const void* dy, const void* x, const void* weight /*nullable*/,
                                 const float* mean, const float* rstd, int64_t rows, int64_t cols,
@@ -228,13 +231,12 @@ int64_t tb200_total_launches(void);
  * non-zero code in a device status word and the kernel still runs to its end. This call
  * synchronises the device and returns that word (0 = healthy); `reset` != 0 clears it. */
 int tb200_device_status(int reset);
-/* Force the CUDA-core kernels (1) or let the dispatcher choose (0). Used by tests to
- * cross-check the tensor-core kernels against the simple ones. Returns the old value. */
-int tb200_set_force_simt(int on);
 /* The norm backward kernels fold their per-CTA weight/bias gradient rows inside the same
  * (cooperative) launch when on != 0 (the default), or in a second finalize kernel when
  * on == 0. Both orders of summation are fixed. Used by tests to cover both paths (the
- * second is otherwise only taken when the grid cannot be co-resident). Returns the old value. */
+ * second is otherwise only taken when the grid cannot be co-resident). The setting belongs to
+ * the calling thread and applies to the norm backward calls that thread makes; other threads
+ * keep their own. Returns the old value. */
 int tb200_set_norm_fused_finalize(int on);
 
 #ifdef __cplusplus

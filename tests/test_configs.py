@@ -16,7 +16,7 @@ import torch
 import trident_b200 as trident
 from oracle import torch_oracle
 from tests import util
-from trident_b200.workloads import WORKLOADS
+from workloads import WORKLOADS
 
 pytestmark = pytest.mark.gpu
 

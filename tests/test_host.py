@@ -5,7 +5,8 @@ import pytest
 import torch
 
 import trident_b200 as trident
-from trident_b200 import _lib, util, workloads
+import workloads
+from trident_b200 import _lib, util
 from trident_b200.operation.masked_softmax import as_byte_mask
 from trident_b200.operation.rms_norm import partial_size
 

@@ -10,16 +10,6 @@ from tests import util
 pytestmark = pytest.mark.gpu
 
 
-@pytest.fixture(params=["fused", "two_kernels"])
-def finalize_mode(request):
-    """Runs a backward test with the weight/bias gradient folded inside the main launch and
-    with the separate finalize kernel."""
-    from trident_b200 import _lib
-
-    old = _lib.set_norm_fused_finalize(request.param == "fused")
-    yield request.param
-    _lib.set_norm_fused_finalize(old)
-
 # tolerance for fp32 norms: rtol = atol = 1e-5
 RTOL = ATOL = 1e-5
 
@@ -39,7 +29,7 @@ def test_forward(y_size, x_size, affine, device):
 
 @pytest.mark.parametrize("y_size, x_size", [(2000, 4), (4, 2000), (300, 1024), (33, 4096), (70, 8192)])
 @pytest.mark.parametrize("affine", ["none", "both", "weight"])
-def test_backward(y_size, x_size, affine, device, finalize_mode):
+def test_backward(y_size, x_size, affine, device):
     x = util.randn(y_size, x_size, seed=1)
     dy = util.randn(y_size, x_size, seed=4)
     w = util.randn(x_size, seed=2) if affine in ("weight", "both") else None

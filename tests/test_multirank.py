@@ -19,7 +19,7 @@ def _worker(rank, world, port, out):
     dist.init_process_group("gloo", rank=rank, world_size=world)
     import bench
     from oracle import torch_oracle
-    from trident_b200 import workloads
+    import workloads
 
     assert bench.dist_env() == (rank, rank, world)
     wl = workloads.WORKLOADS["layer_norm"]
@@ -48,7 +48,7 @@ def test_two_ranks_gloo(tmp_path):
     assert got["t_max"] == 2.0  # max over ranks
     sys.path.insert(0, ROOT)
     from oracle import torch_oracle
-    from trident_b200 import workloads
+    import workloads
 
     wl = workloads.WORKLOADS["layer_norm"]
     whole = wl.make(0, 1, "cpu", scale=8)

@@ -10,16 +10,6 @@ from tests import util
 pytestmark = pytest.mark.gpu
 
 
-@pytest.fixture(params=["fused", "two_kernels"])
-def finalize_mode(request):
-    """Runs a backward test with the weight/bias gradient folded inside the main launch and
-    with the separate finalize kernel."""
-    from trident_b200 import _lib
-
-    old = _lib.set_norm_fused_finalize(request.param == "fused")
-    yield request.param
-    _lib.set_norm_fused_finalize(old)
-
 RTOL = ATOL = 1e-5
 
 
@@ -42,7 +32,7 @@ def test_forward(y_size, x_size, p, device):
 
 @pytest.mark.parametrize("y_size, x_size, p", [(1000, 10, 0.5), (10, 1000, 1.0), (200, 4096, -1.0), (90, 1024, 0.5)])
 @pytest.mark.parametrize("with_bias", [False, True])
-def test_backward(y_size, x_size, p, with_bias, device, finalize_mode):
+def test_backward(y_size, x_size, p, with_bias, device):
     x = util.randn(y_size, x_size, seed=1)
     w = util.randn(x_size, seed=2)
     b = util.randn(x_size, seed=3) if with_bias else None

@@ -47,7 +47,15 @@ def _static(x, dy, w, mean, rstd):
 
 @pytest.mark.parametrize(
     "rows, cols, dtype",
-    [(4096, 1024, torch.float32), (513, 4096, torch.bfloat16), (300, 8192, torch.float16), (70, 36, torch.float32)],
+    [
+        (4096, 1024, torch.float32),
+        (513, 4096, torch.bfloat16),
+        (300, 8192, torch.float16),
+        (70, 36, torch.float32),
+        # 2048 vectors per row: beyond the grouped kernel, and more rows than the 2 MiB array holds
+        # partial rows for (32 of [2, 8192] floats), so the grid is cut down to what fits
+        (64, 8192, torch.float32),
+    ],
 )
 def test_matches_regular_entry_point_on_two_calls_in_a_row(rows, cols, dtype, device):
     first = _problem(rows, cols, dtype, device, seed=1)
@@ -84,3 +92,31 @@ def test_rejects_rows_wider_than_the_built_in_scratch(device):
     x, dy, w, mean, rstd = _problem(4, 8192 + 8, torch.float32, device, seed=4)
     with pytest.raises(_lib.Tb200Error, match="exceed the built-in scratch"):
         _static(x, dy, w, mean, rstd)
+
+
+@pytest.mark.parametrize("which", ["weight_only", "bias_only"])
+@pytest.mark.parametrize("rows, cols", [(300, 1024), (64, 8192)])
+def test_one_column_gradient_only(which, rows, cols, device):
+    x, dy, w, mean, rstd = _problem(rows, cols, torch.float32, device, seed=5)
+    want = _regular(x, dy, w, mean, rstd)
+    dx, g = torch.empty_like(x), torch.empty_like(w)
+    if which == "weight_only":
+        _lib.layer_norm_bwd_static(dx, g, None, dy, x, w, mean, rstd, rows, cols)
+    else:
+        _lib.layer_norm_bwd_static(dx, None, g, dy, x, w, mean, rstd, rows, cols)
+    tol = 1e-5 * max(1.0, rows ** 0.5)
+    assert torch.allclose(dx, want[0], rtol=1e-5, atol=1e-5)
+    assert torch.allclose(g, want[1 if which == "weight_only" else 2], rtol=1e-5, atol=tol)
+
+
+def test_empty_problem_zero_fills_like_the_regular_entry_point(device):
+    cols = 256
+    dw = torch.full((cols,), 7.0, device=device)
+    db = torch.full((cols,), 7.0, device=device)
+    stream = torch.cuda.current_stream(dw.device).cuda_stream
+    rc = _lib.load().tb200_layer_norm_bwd_static(
+        None, dw.data_ptr(), db.data_ptr(), None, None, None, None, None, 0, cols, _lib.dtype_code(dw.dtype), stream
+    )
+    assert rc == 0, _lib.last_error()
+    torch.cuda.synchronize()
+    assert (dw == 0).all() and (db == 0).all()

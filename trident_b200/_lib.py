@@ -28,7 +28,6 @@ SIGNATURES = {
     "tb200_device_check": (c_int, [c_int]),
     "tb200_last_kernel": (ctypes.c_char_p, []),
     "tb200_last_launch_count": (c_int, []),
-    "tb200_set_force_simt": (c_int, [c_int]),
     "tb200_set_norm_fused_finalize": (c_int, [c_int]),
     "tb200_total_launches": (c_i64, []),
     "tb200_device_status": (c_int, [c_int]),
@@ -107,10 +106,6 @@ def total_launches():
 def device_status(reset=False):
     """Synchronises and returns the tensor-core kernels' status word (0 = healthy)."""
     return load().tb200_device_status(1 if reset else 0)
-
-
-def set_force_simt(on):
-    return load().tb200_set_force_simt(1 if on else 0)
 
 
 def set_norm_fused_finalize(on):

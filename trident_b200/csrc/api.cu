@@ -14,7 +14,6 @@ namespace tb200 {
 static thread_local char g_error[512] = "";
 static thread_local const char* g_kernel = "";
 static thread_local int g_launches = 0;
-static int g_force_simt = 0;
 static std::atomic<long long> g_total_launches{0};
 
 void set_error(const char* fmt, ...) {
@@ -32,7 +31,6 @@ void add_launches(int launches) {
   g_launches += launches;
   g_total_launches += launches;
 }
-bool force_simt() { return g_force_simt != 0; }
 
 int sm_count() {
   static int cached[64];
@@ -63,11 +61,6 @@ extern "C" int tb200_version(void) { return 100; }
 extern "C" const char* tb200_last_kernel(void) { return g_kernel; }
 extern "C" int tb200_last_launch_count(void) { return g_launches; }
 extern "C" int64_t tb200_total_launches(void) { return (int64_t)g_total_launches.load(); }
-extern "C" int tb200_set_force_simt(int on) {
-  const int old = g_force_simt;
-  g_force_simt = on;
-  return old;
-}
 
 extern "C" int tb200_device_check(int device) {
   int major = 0;
@@ -102,7 +95,7 @@ extern "C" int tb200_linear_fwd(void* y, const void* x, const void* w, const voi
   if (B * M * N == 0) return 0;  // nothing to write (empty tensors may come with null pointers)
   TB200_REQUIRE(y && x && w, TB200_ERR_INVALID, "linear_fwd: null pointer");
   cudaStream_t st = (cudaStream_t)stream;
-  if (!force_simt()) {
+  {
     // y[(b,m), n] = sum_k x[(b,m), k] w[n, k]: batch folds into M when x is batch-collapsible
     if (dtype != TB200_F32 && x_sk == 1 && w_sk == 1 && (B == 1 || x_sb == M * x_sm)) {
       TcGemmArgs g;
@@ -136,7 +129,7 @@ extern "C" int tb200_linear_bwd_input(void* dx, const void* dy, const void* w, i
   if (B * M * K == 0) return 0;
   TB200_REQUIRE(dx && dy && w, TB200_ERR_INVALID, "linear_bwd_input: null pointer");
   cudaStream_t st = (cudaStream_t)stream;
-  if (!force_simt()) {
+  {
     // dx[(b,m), k] = sum_n dy[(b,m), n] w[n, k]: the reduction index n is dy's contiguous
     // one (K-major A) and w's row index (MN-major B).
     if (dtype != TB200_F32 && dx_sk == 1 && w_sk == 1 && (B == 1 || dx_sb == M * dx_sm)) {
@@ -172,7 +165,7 @@ extern "C" int tb200_linear_bwd_weight(void* dw, const void* dy, const void* x, 
     return zero_fill(dw, (size_t)N * K * dtype_size(dtype), (cudaStream_t)stream, "linear_bwd_weight");
   TB200_REQUIRE(dw && dy && x, TB200_ERR_INVALID, "linear_bwd_weight: null pointer");
   cudaStream_t st = (cudaStream_t)stream;
-  if (!force_simt()) {
+  {
     // dw[n, k] = sum_{(b,m)} dy[(b,m), n] x[(b,m), k]: both operands are MN-major.
     if (dtype != TB200_F32 && x_sk == 1 && (B == 1 || x_sb == M * x_sm)) {
       TcGemmArgs g;
@@ -208,7 +201,7 @@ extern "C" int tb200_geglu_fwd(void* out, void* state_gate, const void* x, const
   TB200_REQUIRE(out && state_gate && x && w, TB200_ERR_INVALID, "geglu_fwd: null pointer");
   TB200_REQUIRE(N % 2 == 0, TB200_ERR_INVALID, "geglu_fwd: N=%lld must be even", (long long)N);
   cudaStream_t st = (cudaStream_t)stream;
-  if (!force_simt()) {
+  {
     if (dtype != TB200_F32 && x_sk == 1 && w_sk == 1 && (B == 1 || x_sb == M * x_sm)) {
       TcGemmArgs g;
       g.M = B * M; g.N = N; g.K = K;
@@ -268,7 +261,7 @@ extern "C" int tb200_attention_fwd(void* out, float* lse, const void* q, const v
                          out_strides, mask, mask_strides, is_causal, softmax_scale))
     return rc;
   cudaStream_t st = (cudaStream_t)stream;
-  if (!force_simt() && attn_tc_supported(a, dtype, q, k, v, out)) {
+  if (attn_tc_supported(a, dtype, q, k, v, out)) {
     int rc = launch_attn_fwd_tc(out, lse, q, k, v, mask, a, dtype, st);
     if (rc == 0) note_kernel("attn_tcgen05", 1);
     return rc;
@@ -310,7 +303,7 @@ extern "C" int tb200_attention_bwd(void* dq, void* dk, void* dv, void* dmask, co
   TB200_REQUIRE(workspace_bytes >= (size_t)B * H * S * sizeof(float), TB200_ERR_WORKSPACE,
                 "attention_bwd: workspace too small");
   cudaStream_t st = (cudaStream_t)stream;
-  if (!force_simt() && !dmask && attn_tc_supported(a, dtype, q, k, v, out) && aligned16(dout) &&
+  if (!dmask && attn_tc_supported(a, dtype, q, k, v, out) && aligned16(dout) &&
       aligned16(dq) && aligned16(dk) && aligned16(dv)) {
     const size_t row_bytes = attn_row_scratch_bytes(B, H, S);
     const size_t need = row_bytes + (size_t)B * H * S * D * sizeof(float);

@@ -114,17 +114,6 @@ __device__ inline void unpack_pair<__half>(uint32_t v, float& lo, float& hi) {
   hi = f.y;
 }
 
-#ifdef TB200_ATTN_PROFILE
-__device__ long long g_prof[64];
-#define PROF_DECL long long prof_acc[12] = {0}; long long prof_last = clock64(); const bool prof_on = blockIdx.x == 0 && blockIdx.y == 0;
-#define PROF(slot) do { if (prof_on) { long long t_ = clock64(); prof_acc[slot] += t_ - prof_last; prof_last = t_; } } while (0)
-#define PROF_FLUSH(role) do { if (prof_on) for (int i_ = 0; i_ < 12; ++i_) g_prof[(role) * 16 + i_] = prof_acc[i_]; } while (0)
-#else
-#define PROF_DECL
-#define PROF(slot)
-#define PROF_FLUSH(role)
-#endif
-
 template <typename T, int D, bool CAUSAL, bool MASKED>
 __global__ void __launch_bounds__(bwd_threads_for(D, MASKED), 1)
     attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
@@ -284,7 +273,6 @@ __global__ void __launch_bounds__(bwd_threads_for(D, MASKED), 1)
     ptx::tc_fence_after();
     issue_st(0);
     ptx::umma_commit(st_ready);
-    PROF_DECL
     for (int s = 0; s < steps; ++s) {
       const int st = s & 1;
       const uint32_t ph = s & 1;
@@ -292,7 +280,6 @@ __global__ void __launch_bounds__(bwd_threads_for(D, MASKED), 1)
       const uint32_t da = ptx::smem_u32(do_smem + st * TILE_BYTES);
       // dP^T(s) = V_j dO^T: its columns still hold dQ(s-1) until the drain warps are done
       if (s > 0) ptx::mbar_wait(dq_drained, ph ^ 1, abort_flag, p.status, 44);
-      PROF(0);
       ptx::tc_fence_after();
 #pragma unroll
       for (int ks = 0; ks < D / 16; ++ks) {
@@ -302,9 +289,7 @@ __global__ void __launch_bounds__(bwd_threads_for(D, MASKED), 1)
       }
       ptx::umma_commit(dpt_ready);
       // dV += P^T dO (reduction over the 128 query rows of the tile)
-      PROF(1);
       ptx::mbar_wait(p1_ready, ph, abort_flag, p.status, 45);
-      PROF(2);
       ptx::tc_fence_after();
 #pragma unroll
       for (int ks = 0; ks < 8; ++ks)
@@ -312,17 +297,13 @@ __global__ void __launch_bounds__(bwd_threads_for(D, MASKED), 1)
                      ptx::make_smem_desc(da + ks * 2048, BOX_BYTES, 1024), IDESC_DKV, (s | ks) != 0);
       // S^T(s+1): overwrites P^T(s), which the dV products above read first (in-order pipe)
       if (s + 1 < steps) {
-        PROF(3);
         ptx::mbar_wait(&qdo_full[st ^ 1], ((s + 1) >> 1) & 1, abort_flag, p.status, 46);
-        PROF(4);
         ptx::tc_fence_after();
         issue_st(st ^ 1);
         ptx::umma_commit(st_ready);
       }
       // dK += dS^T Q, then dQ = dS K into the dP^T columns
-      PROF(5);
       ptx::mbar_wait(p2_ready, ph, abort_flag, p.status, 47);
-      PROF(6);
       ptx::tc_fence_after();
 #pragma unroll
       for (int ks = 0; ks < 8; ++ks)
@@ -341,9 +322,7 @@ __global__ void __launch_bounds__(bwd_threads_for(D, MASKED), 1)
                        ptx::make_smem_desc(ka + ks * 2048, BOX_BYTES, 1024), IDESC_DQ, ks != 0);
       }
       ptx::umma_commit(dq_ready);
-      PROF(7);
     }
-    PROF_FLUSH(0);
     ptx::umma_commit(all_done);
   } else if (warp >= 4 && warp < DRAIN_WARP0) {
     // ---------------------------------------------------------------- P^T / dS^T (lane = key row)
@@ -361,18 +340,14 @@ __global__ void __launch_bounds__(bwd_threads_for(D, MASKED), 1)
     if constexpr (MASKED)
       mask_col = reinterpret_cast<const T*>(p.mask) + (long long)b * p.a.ms[0] + (long long)h * p.a.ms[1] +
                  (long long)kv_g * p.a.ms[3];
-    PROF_DECL
     for (int s = 0; s < steps; ++s) {
       const int it = i_begin + (s + jt) % steps;  // staggered start: CTAs of one head add into different dQ tiles
       const int st = s & 1;
       const float4* nlse4 = reinterpret_cast<const float4*>(nlse_smem + st * 128);
       const float4* ndel4 = reinterpret_cast<const float4*>(ndelta_smem + st * 128);
       uint32_t pp[NCH * 16];  // this thread's part of a P^T row, packed pairs along the query index
-      PROF(0);
       ptx::mbar_wait(&qdo_full[st], (s >> 1) & 1, abort_flag, p.status, 48);  // -lse, -delta of the tile
-      PROF(1);
       ptx::mbar_wait(st_ready, s & 1, abort_flag, p.status, 49);
-      PROF(2);
       ptx::tc_fence_after();
       const bool diag = CAUSAL && (it == jt);
       // ---- stage A: P^T = exp2(S^T * scale*log2e - lse*log2e)
@@ -418,20 +393,15 @@ __global__ void __launch_bounds__(bwd_threads_for(D, MASKED), 1)
         };
         ptx::tmem_ld32(st_addr + c0 * 32, ra);
         am::tmem_ld_wait_dep(ra);
-        PROF(3);
         if constexpr (NCH == 2) ptx::tmem_ld32(st_addr + c0 * 32 + 32, rb);
         stage_a(ra, c0, 0);
         if constexpr (NCH == 2) {
-          PROF(4);
           am::tmem_ld_wait_dep(rb);
-          PROF(0);
           stage_a(rb, c0 + 1, 1);
         }
         // all owners of a key row (this warp and its partners four warps apart) must have read
         // their S^T columns before any of them overwrites them with packed P^T
-        PROF(4);
         asm volatile("bar.sync 1, %0;" ::"n"(COMPUTE_WARPS * 32) : "memory");
-        PROF(5);
 #pragma unroll
         for (int lc = 0; lc < NCH; ++lc) {
           uint32_t chunk[16];
@@ -442,11 +412,9 @@ __global__ void __launch_bounds__(bwd_threads_for(D, MASKED), 1)
         ptx::tmem_st_wait();
         ptx::tc_fence_before();
         ptx::mbar_arrive(p1_ready);
-        PROF(6);
       }
       // ---- stage B: dS^T = P^T (dP^T - delta)
       ptx::mbar_wait(dpt_ready, s & 1, abort_flag, p.status, 50);
-      PROF(7);
       ptx::tc_fence_after();
       {
         uint32_t ra[32];
@@ -484,16 +452,13 @@ __global__ void __launch_bounds__(bwd_threads_for(D, MASKED), 1)
         };
         ptx::tmem_ld32(dp_addr + c0 * 32, ra);
         am::tmem_ld_wait_dep(ra);
-        PROF(8);
         if constexpr (NCH == 2) ptx::tmem_ld32(dp_addr + c0 * 32 + 32, rb);
         stage_b(ra, c0, 0);
         if constexpr (NCH == 2) {
           am::tmem_ld_wait_dep(rb);
           stage_b(rb, c0 + 1, 1);
         }
-        PROF(9);
         asm volatile("bar.sync 1, %0;" ::"n"(COMPUTE_WARPS * 32) : "memory");  // dP^T fully read before dS^T overwrites it
-        PROF(10);
 #pragma unroll
         for (int lc = 0; lc < NCH; ++lc) {
           uint32_t chunk[16];
@@ -505,10 +470,8 @@ __global__ void __launch_bounds__(bwd_threads_for(D, MASKED), 1)
         ptx::fence_proxy_async_smem();
         ptx::tc_fence_before();
         ptx::mbar_arrive(p2_ready);
-        PROF(11);
       }
     }
-    if (threadIdx.x == 4 * 32) PROF_FLUSH(1);
     // epilogue: dV and dK rows of this key tile
     ptx::mbar_wait(all_done, 0, abort_flag, p.status, 51);
     ptx::tc_fence_after();
@@ -543,12 +506,9 @@ __global__ void __launch_bounds__(bwd_threads_for(D, MASKED), 1)
     const int r = quarter * 32 + lane;
     const uint32_t dq_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + COL_DQ;
     const long long row_base = ((long long)b * p.a.H + h) * p.a.S;
-    PROF_DECL
     for (int s = 0; s < steps; ++s) {
       const int it = i_begin + (s + jt) % steps;  // staggered start: CTAs of one head add into different dQ tiles
-      PROF(0);
       ptx::mbar_wait(dq_ready, s & 1, abort_flag, p.status, 52);
-      PROF(1);
       ptx::tc_fence_after();
       if constexpr (DQ_T) {
         // lane = feature d: this thread owns feature d = r of the tile's 128 query rows
@@ -569,14 +529,12 @@ __global__ void __launch_bounds__(bwd_threads_for(D, MASKED), 1)
         am::tmem_ld_wait_dep(r0);
         ptx::tc_fence_before();
         ptx::mbar_arrive(dq_drained);  // tensor memory released as soon as its values sit in registers
-        PROF(2);
 #pragma unroll
         for (int i = 0; i < 32; ++i) red_add_f32(dst + (long long)(32 + i) * D, __uint_as_float(r1[i]));
 #pragma unroll
         for (int i = 0; i < 32; ++i) red_add_f32(dst + (long long)(64 + i) * D, __uint_as_float(r2[i]));
 #pragma unroll
         for (int i = 0; i < 32; ++i) red_add_f32(dst + (long long)(96 + i) * D, __uint_as_float(r0[i]));
-        PROF(3);
       } else {
         // lane = query row; dQ_i leaves through a staging tile of D/32 boxes of [128 rows][32
         // floats] (16 KB each) and bulk tensor reduce-add copies
@@ -588,7 +546,6 @@ __global__ void __launch_bounds__(bwd_threads_for(D, MASKED), 1)
         am::tmem_ld_wait_dep(r1);
         ptx::tc_fence_before();
         ptx::mbar_arrive(dq_drained);  // tensor memory released as soon as its values sit in registers
-        PROF(2);
         // the copies of the previous tile must have read the staging tile before it is rewritten
         if (threadIdx.x == DRAIN_WARP0 * 32) bulk_wait_group_read0();
         asm volatile("bar.sync 2, 128;" ::: "memory");
@@ -608,11 +565,9 @@ __global__ void __launch_bounds__(bwd_threads_for(D, MASKED), 1)
           tma_reduce_add_2d(&map_dq, dq_stage + 16384, 32, y);
           bulk_commit_group();
         }
-        PROF(3);
       }
     }
     if (threadIdx.x == DRAIN_WARP0 * 32) bulk_wait_group0();  // every reduce-add has landed before the CTA ends
-    if (threadIdx.x == DRAIN_WARP0 * 32) PROF_FLUSH(2);
   }
   ptx::tc_fence_before();
   __syncthreads();
@@ -707,9 +662,8 @@ static int launch_bwd(const CUtensorMap& mq, const CUtensorMap& mk, const CUtens
   constexpr int SMEM = 6 * 128 * D * 2 + 128 * 128 * 2 + 2048 + 128 + ((MASKED && D == 64) ? 2 * 128 * 128 * 2 : 0) +
                        (D == 64 ? 128 * D * 4 : 0);
   auto kern = attn_bwd_tc_kernel<T, D, CAUSAL, MASKED>;
-  static std::once_flag once;
-  static cudaError_t attr_err = cudaSuccess;
-  std::call_once(once, [&] { attr_err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM); });
+  static std::atomic<unsigned long long> optin_done{0};
+  const cudaError_t attr_err = smem_optin_per_device(optin_done, reinterpret_cast<const void*>(kern), SMEM);
   if (attr_err != cudaSuccess) {
     set_error("attention_bwd: cudaFuncSetAttribute failed: %s", cudaGetErrorString(attr_err));
     return (int)attr_err;
@@ -792,9 +746,3 @@ int launch_attn_bwd_tc(void* dq, void* dk, void* dv, const void* dout, const voi
 }
 
 }  // namespace tb200
-
-#ifdef TB200_ATTN_PROFILE
-extern "C" int tb200_debug_read_prof(long long* out) {
-  return (int)cudaMemcpyFromSymbol(out, tb200::g_prof, sizeof(long long) * 64);
-}
-#endif

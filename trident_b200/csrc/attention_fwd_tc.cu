@@ -11,9 +11,9 @@
 //               S_t = Q_t K_j^T  (both operands K-major in smem),
 //               O_t += P_t V_j (P_t read from tensor memory, V_j MN-major in smem)
 //   warp 2      tensor-memory allocation
-//   warp 3      at D = 64 with a mask: producer of the [128 q][128 kv] mask tiles (one shared-memory
-//               buffer per query tile; the softmax threads copy their row segment to registers,
-//               fence, and hand the buffer back)
+//   warp 3      at D = 64 with a mask: producer of the [128 q][128 kv] mask tiles (a two-stage ring of
+//               shared-memory buffers per query tile; a softmax thread reads its row segment from the
+//               buffer while it scales the scores and hands the stage back after the last use)
 //   warps 4-7   softmax of query tile 0, warps 8-11 of query tile 1: one thread per score
 //               row; row maximum and sum need no shuffles. The 128 scores of the row are read
 //               from tensor memory once and stay in registers between the maximum and the
@@ -53,14 +53,6 @@ constexpr int REGS_LAUNCH = 168, REGS_SERVICE = 56, REGS_SOFTMAX = 224;
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr float LN2 = 0.6931471805599453f;
 constexpr float RESCALE_THRESHOLD = 8.f;
-// Out of every four element pairs, this many take their exponential from the FMA-pipe
-// polynomial instead of the MUFU unit (see am::ex2_poly2). Measured on B200 at 2 of 4 the
-// forward pass was 9 % slower than at 0: the softmax warps are bound by instruction issue,
-// not by the MUFU rate, so the default keeps every exponential on MUFU.
-#ifndef TB200_POLY_EXP_QUARTERS
-#define TB200_POLY_EXP_QUARTERS 0
-#endif
-constexpr int POLY_EXP_QUARTERS = TB200_POLY_EXP_QUARTERS;
 
 struct FwdParams {
   AttnArgs a;
@@ -129,24 +121,13 @@ __device__ inline void load_mask32(float (&mv)[32], const T* row, long long col,
   }
 }
 
-#ifdef TB200_ATTN_PROFILE
-__device__ long long g_prof_fwd[64];
-#define PROF_DECL long long prof_acc[12] = {0}; long long prof_last = clock64(); const bool prof_on = blockIdx.x == 0 && blockIdx.y == 0;
-#define PROF(slot) do { if (prof_on) { long long t_ = clock64(); prof_acc[slot] += t_ - prof_last; prof_last = t_; } } while (0)
-#define PROF_FLUSH(role) do { if (prof_on) for (int i_ = 0; i_ < 12; ++i_) g_prof_fwd[(role) * 16 + i_] = prof_acc[i_]; } while (0)
-#else
-#define PROF_DECL
-#define PROF(slot)
-#define PROF_FLUSH(role)
-#endif
-
 template <typename T, int D, bool CAUSAL, bool MASKED>
 __global__ void __launch_bounds__(FWD_THREADS, 1)
     attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                        const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_mask,
                        const FwdParams p) {
   constexpr int TILE_BYTES = 128 * D * 2;
-  // At D = 64 there is shared memory left for one [128 q][128 kv] mask tile per query tile: a
+  // At D = 64 there is shared memory left for two [128 q][128 kv] mask tiles per query tile: a
   // thread's row segment then comes from shared memory (conflict-free 16-byte reads of the
   // 128-byte swizzled boxes) instead of 16 global loads that each touch 32 different lines per warp.
   constexpr bool MASK_SMEM = MASKED && D == 64;
@@ -169,8 +150,24 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
   uint8_t* q_smem = smem;                       // [2][TILE_BYTES]
   uint8_t* k_smem = smem + 2 * TILE_BYTES;      // [2][TILE_BYTES]
   uint8_t* v_smem = smem + 4 * TILE_BYTES;      // [2][TILE_BYTES]
-  uint8_t* mask_smem = smem + 6 * TILE_BYTES;   // [2][MASK_TILE_BYTES] when MASK_SMEM
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 6 * TILE_BYTES + (MASK_SMEM ? 2 * MASK_TILE_BYTES : 0));
+  uint8_t* mask_smem = smem + 6 * TILE_BYTES;   // [2 query tiles][2 stages][MASK_TILE_BYTES] when MASK_SMEM
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 6 * TILE_BYTES + (MASK_SMEM ? 4 * MASK_TILE_BYTES : 0));
+  // Hand-overs (j = key tile, t = query tile; every barrier completes once per j, so a waiter of
+  // phase j passes parity j & 1 and no barrier can run two phases ahead of its waiter):
+  //   barrier     arriver, after                                waiter, before                      ordering
+  //   k/v_full    bulk copy (complete_tx)                       MMA: QK^T / P V read the stage      async proxy on both sides
+  //   k/v_empty   tcgen05.commit after the last product that    producer: next copy into the stage  commit = products done reading
+  //               reads the stage
+  //   s_full[t]   tcgen05.commit after Q_t K_j^T                softmax: tcgen05.ld of S_t          fence::after_thread_sync
+  //   s_free[t]   128 softmax threads after wait::ld of S_t(j)  MMA: Q_t K_{j+1}^T over S_t         fence::before / ::after
+  //               (D = 64 only; at D = 128 the product follows P V(j) on the in-order pipe)
+  //   p_full[t]   128 softmax threads after wait::st of P_t(j)  MMA: P_t V_j                        fence::before / ::after
+  //               (and of the rescaled O_t)
+  //   o_done[t]   tcgen05.commit after P_t V_j                  softmax: rescale of O_t, P_t(j+1)   fence::after_thread_sync
+  //               over P_t(j) (D = 64), final read of O_t
+  //   mask_full   bulk copy (complete_tx)                       softmax: ld.shared of its row       mbarrier acquire
+  //   mask_empty  128 softmax threads after the values were     mask producer: next copy            fence.proxy.async + release
+  //               consumed
   uint64_t* q_full = bars;         // [2]
   uint64_t* k_full = bars + 2;     // [2]
   uint64_t* k_empty = bars + 4;    // [2]
@@ -179,10 +176,10 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
   uint64_t* s_full = bars + 10;    // [2]  MMA -> softmax: scores ready
   uint64_t* p_full = bars + 12;    // [2]  softmax -> MMA: probabilities written
   uint64_t* o_done = bars + 14;    // [2]  MMA -> softmax: P V accumulated
-  uint64_t* mask_full = bars + 16;   // [2]  mask producer -> softmax of query tile t
-  uint64_t* mask_empty = bars + 18;  // [2]  softmax -> mask producer: tile copied to registers
-  uint64_t* s_free = bars + 20;      // [2]  softmax -> MMA: scores read into registers (P_SPLIT)
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 22);
+  uint64_t* s_free = bars + 16;      // [2]  softmax -> MMA: scores read into registers (P_SPLIT)
+  uint64_t* mask_full = bars + 18;   // [2 tiles][2 stages]  mask producer -> softmax of query tile t
+  uint64_t* mask_empty = bars + 22;  // [2 tiles][2 stages]  softmax -> mask producer: last read done
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 26);
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -211,10 +208,10 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
     ptx::mbar_init(&p_full[1], 128);
     ptx::mbar_init(&o_done[0], 1);
     ptx::mbar_init(&o_done[1], 1);
-    ptx::mbar_init(&mask_full[0], 1);
-    ptx::mbar_init(&mask_full[1], 1);
-    ptx::mbar_init(&mask_empty[0], 128);
-    ptx::mbar_init(&mask_empty[1], 128);
+    for (int i = 0; i < 4; ++i) {
+      ptx::mbar_init(&mask_full[i], 1);
+      ptx::mbar_init(&mask_empty[i], 128);
+    }
     ptx::mbar_init(&s_free[0], 128);
     ptx::mbar_init(&s_free[1], 128);
     *abort_flag = 0;
@@ -270,20 +267,28 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
     }
   } else if (MASK_SMEM && warp == 3 && lane == 0) {
     // ---------------------------------------------------------------- mask producer
-    // One buffer per query tile: the softmax threads copy their row segment to registers as
-    // soon as the tile has landed and hand the buffer back, so the next tile's copy is in
-    // flight while they work on the scores of the current one.
+    // Two stages per query tile: the copy of key tile j + 1 is in flight while the softmax
+    // threads of the tile read key tile j's stage. Stage j & 1 holds key tile j; its k-th use
+    // (k = j >> 1) is phase k of both of its barriers.
+    //   mask_empty -> this thread: 128 softmax threads arrived after their last ld.shared of the
+    //     stage had returned its value (the arrive follows instructions that consume it) and after a
+    //     fence.proxy.async, since the next access to the stage is this bulk copy (async proxy).
+    //   mask_full -> softmax threads: completes when the copy's bytes have landed (complete_tx).
     if (p.mask_tma) {
       for (int j = 0; j < nmax; ++j) {
+        const int stg = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
 #pragma unroll
         for (int t = 0; t < 2; ++t) {
           if (j < (t == 0 ? n0 : n1)) {
-            ptx::mbar_wait(&mask_empty[t], (j & 1) ^ 1, abort_flag, p.status, 13 + t);
-            ptx::mbar_expect_tx(&mask_full[t], MASK_TILE_BYTES);
+            uint64_t* full = &mask_full[t * 2 + stg];
+            uint8_t* dst = mask_smem + (t * 2 + stg) * MASK_TILE_BYTES;
+            ptx::mbar_wait(&mask_empty[t * 2 + stg], ph ^ 1, abort_flag, p.status, 13 + t);
+            ptx::mbar_expect_tx(full, MASK_TILE_BYTES);
 #pragma unroll
             for (int c = 0; c < 2; ++c)
-              tma_load_4d(mask_smem + t * MASK_TILE_BYTES + c * BOX_BYTES, &map_mask, &mask_full[t], j * TK + c * 64,
-                          (t == 0 ? qt0 : qt1) * TQ, p.mask_has_h ? h : 0, p.mask_has_b ? b : 0);
+              tma_load_4d(dst + c * BOX_BYTES, &map_mask, full, j * TK + c * 64, (t == 0 ? qt0 : qt1) * TQ,
+                          p.mask_has_h ? h : 0, p.mask_has_b ? b : 0);
           }
         }
       }
@@ -330,7 +335,6 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
       commit_(&s_full[1]);
     }
     commit_(&k_empty[0]);
-    PROF_DECL
     if constexpr (P_SPLIT) {
       for (int j = 0; j < nmax; ++j) {
         const int st = j & 1, nst = (j + 1) & 1;
@@ -343,21 +347,17 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
           // the last user of a K or V stage releases it: tile 1 when it takes part, else tile 0
           const bool last_k = t == 1 || j + 1 >= no, last_v = t == 1 || j >= no;
           if (j + 1 < nt) {
-            PROF(t * 4 + 0);
             wait_(&s_free[t], jp, 35 + t);
             if (!k_next_ready) wait_(&k_full[nst], nph, 26);
             k_next_ready = true;
-            PROF(t * 4 + 1);
             ptx::tc_fence_after();
             issue_qk(t, nst);
             commit_(&s_full[t]);
             if (last_k) commit_(&k_empty[nst]);
           }
           if (j < nt) {
-            PROF(t * 4 + 2);
             wait_(&p_full[t], jp, 24 + 3 * t);
             wait_(&v_full[st], ph, 25 + 3 * t);
-            PROF(t * 4 + 3);
             ptx::tc_fence_after();
             issue_pv(t, st, j > 0);
             commit_(&o_done[t]);
@@ -372,20 +372,15 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
       const uint32_t jp = j & 1;
       bool k_next_ready = false;
       if (j < n0) {
-        PROF(0);
         wait_(&p_full[0], jp, 24);
-        PROF(1);
         wait_(&v_full[st], ph, 25);
-        PROF(2);
         ptx::tc_fence_after();
         issue_pv(0, st, j > 0);
         commit_(&o_done[0]);
         if (j >= n1) commit_(&v_empty[st]);
       }
       if (j + 1 < n0) {
-        PROF(3);
         wait_(&k_full[nst], nph, 26);
-        PROF(4);
         k_next_ready = true;
         ptx::tc_fence_after();
         issue_qk(0, nst);
@@ -393,9 +388,7 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
         if (j + 1 >= n1) commit_(&k_empty[nst]);
       }
       if (j < n1) {
-        PROF(5);
         wait_(&p_full[1], jp, 27);
-        PROF(6);
         wait_(&v_full[st], ph, 28);
         ptx::tc_fence_after();
         issue_pv(1, st, j > 0);
@@ -409,10 +402,8 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
         commit_(&s_full[1]);
         commit_(&k_empty[nst]);
       }
-      PROF(7);
     }
     }
-    if (elected) PROF_FLUSH(0);
   }
   } else {
     // ---------------------------------------------------------------- softmax + epilogue
@@ -432,42 +423,50 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
       mask_row = reinterpret_cast<const T*>(p.mask) + (long long)b * p.a.ms[0] + (long long)h * p.a.ms[1] +
                  row_g * p.a.ms[2];
     float m_used = -INFINITY, l = 0.f;
-    PROF_DECL
     for (int j = 0; j < n; ++j) {
       const long long kv0 = (long long)j * TK;
-      // the 128 mask values of this row and key tile are fetched before the scores are waited
-      // for, so their latency hides behind the QK^T product (16-byte loads, kept packed)
-      uint4 mraw[MASKED ? 16 : 1];
+      // Mask values of this row and key tile. Staged tiles (D = 64) are read from shared memory
+      // chunk by chunk while the scores are scaled; otherwise the row's 128 values are requested
+      // from global memory before the scores are waited for, so that their latency hides behind
+      // the QK^T product (16-byte loads, kept packed).
+      uint4 mraw[(MASKED && !MASK_SMEM) ? 16 : 1];
+      const bool mask_staged = MASK_SMEM && p.mask_tma;
+      uint32_t mask_row_addr = 0;
       if constexpr (MASKED) {
-        if (MASK_SMEM && p.mask_tma) {
-          ptx::mbar_wait(&mask_full[t], j & 1, abort_flag, p.status, 30);
-          // 16-byte chunk c of row r sits at r * 128 + ((c ^ (r & 7)) << 4) of its [128][64] box
-          const uint32_t row_addr = ptx::smem_u32(mask_smem + t * MASK_TILE_BYTES) + row_in_tile * 128;
+        if (mask_staged) {
+          ptx::mbar_wait(&mask_full[t * 2 + (j & 1)], (j >> 1) & 1, abort_flag, p.status, 30);
+          mask_row_addr = ptx::smem_u32(mask_smem + (t * 2 + (j & 1)) * MASK_TILE_BYTES) + row_in_tile * 128;
+        } else if constexpr (!MASK_SMEM) {
+          if (p.mask_vec) {
 #pragma unroll
-          for (int c = 0; c < 16; ++c) {
-            const uint32_t addr = row_addr + (c >> 3) * BOX_BYTES + (((c & 7) ^ (row_in_tile & 7)) << 4);
-            asm volatile("ld.volatile.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
-                         : "=r"(mraw[c].x), "=r"(mraw[c].y), "=r"(mraw[c].z), "=r"(mraw[c].w)
-                         : "r"(addr)
-                         : "memory");
+            for (int c = 0; c < 16; ++c) mraw[c] = __ldg(reinterpret_cast<const uint4*>(mask_row + kv0 + c * 8));
           }
-          // The buffer is handed back before any loaded value is used: the fence makes the loads
-          // complete first (without it the next tile's copy was seen overwriting rows that had
-          // not been read yet).
-          asm volatile("fence.acq_rel.cta;" ::: "memory");
-          ptx::fence_proxy_async_smem();  // the buffer's next writer is the async proxy (bulk tensor copy)
-          ptx::mbar_arrive(&mask_empty[t]);
-        } else if (p.mask_vec) {
-#pragma unroll
-          for (int c = 0; c < 16; ++c) mraw[c] = __ldg(reinterpret_cast<const uint4*>(mask_row + kv0 + c * 8));
         }
       }
+      // 16-byte group g (0..15) of the row's 128 mask values (mask_vec paths)
+      auto mask_group = [&](int g) -> uint4 {
+        if constexpr (MASK_SMEM) {
+          if (mask_staged) {
+            // chunk g & 7 of row r sits at r * 128 + (((g & 7) ^ (r & 7)) << 4) of box g >> 3
+            uint4 v;
+            const uint32_t addr = mask_row_addr + (g >> 3) * BOX_BYTES + (((g & 7) ^ (row_in_tile & 7)) << 4);
+            asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
+                         : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                         : "r"(addr)
+                         : "memory");
+            return v;
+          }
+          return __ldg(reinterpret_cast<const uint4*>(mask_row + kv0 + g * 8));
+        } else {
+          return mraw[MASKED ? g : 0];
+        }
+      };
       auto mask32 = [&](float (&mv)[32], int c) {
         if (p.mask_vec) {  // (implied by mask_tma)
 #pragma unroll
           for (int jv = 0; jv < 4; ++jv) {
             float f[8];
-            unpack<T>(mraw[MASKED ? c * 4 + jv : 0], f);
+            unpack<T>(mask_group(c * 4 + jv), f);
 #pragma unroll
             for (int i = 0; i < 8; ++i) mv[jv * 8 + i] = f[i] * LOG2E;
           }
@@ -475,9 +474,7 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
           load_mask32<T>(mv, mask_row, kv0 + c * 32, p.a.ms[3], false);
         }
       };
-      PROF(0);
       ptx::mbar_wait(&s_full[t], j & 1, abort_flag, p.status, 31);
-      PROF(1);
       ptx::tc_fence_after();
       const bool diag = CAUSAL && (j == n - 1);
       // The row's 128 scores are read from tensor memory once and stay in registers between
@@ -516,18 +513,18 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
         auto scale32 = [&](uint32_t (&r)[32], int c) {
           if constexpr (MASKED && !CAUSAL) {
             if (p.mask_vec) {
-              // packed path: score * scale + mask * log2(e) on fp32 pairs, two values per maximum
-              const uint64_t scale2 = am::pack2f(p.scale_log2, p.scale_log2), log2e2 = am::pack2f(LOG2E, LOG2E);
+              // packed path: score * scale + mask on fp32 pairs (natural units; log2(e) is applied
+              // with the subtraction of the maximum in pass 2), two values per maximum
+              const uint64_t scale2 = am::pack2f(p.a.scale, p.a.scale);
               float mx1 = -INFINITY;
 #pragma unroll
               for (int jv = 0; jv < 4; ++jv) {
                 uint64_t m2[4];
-                pairs8<T>(mraw[MASKED ? c * 4 + jv : 0], m2);
+                pairs8<T>(mask_group(c * 4 + jv), m2);
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
                   const int idx = jv * 8 + i * 2;
-                  const uint64_t sc =
-                      am::fma2(am::pack2u(r[idx], r[idx + 1]), scale2, am::mul2(m2[i], log2e2));
+                  const uint64_t sc = am::fma2(am::pack2u(r[idx], r[idx + 1]), scale2, m2[i]);
                   float a, b;
                   am::unpack2f(sc, a, b);
                   if (i & 1) mx1 = am::max3(mx1, a, b);
@@ -563,8 +560,19 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
         scale32(sr[2], 2);
         am::tmem_ld_wait_dep(sr[3]);
         scale32(sr[3], 3);
+        if constexpr (MASKED) {
+          if (p.mask_vec) mx *= LOG2E;  // the packed path works in natural units
+        }
+        if constexpr (MASK_SMEM) {
+          if (mask_staged) {
+            // Last read of the mask stage: every ld.shared above has returned its value (the
+            // arithmetic of scale32 consumed it) before this arrive is issued. The stage's next
+            // access is a bulk tensor copy, hence the proxy fence ahead of the release.
+            ptx::fence_proxy_async_smem();
+            ptx::mbar_arrive(&mask_empty[t * 2 + (j & 1)]);
+          }
+        }
       }
-      PROF(2);
       if constexpr (P_SPLIT) {
         // the scores are in registers: the score columns may take the next product
         ptx::tc_fence_before();
@@ -595,10 +603,12 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
         }
       }
       const float m_safe = m_used == -INFINITY ? 0.f : m_used;
-      PROF(3);
       // pass 2: probabilities, row sum, P written as packed 16-bit pairs (over S, or to its own columns)
       {
-        const uint64_t scale2 = plain ? am::pack2f(p.scale_log2, p.scale_log2) : am::pack2f(1.f, 1.f);
+        // registers hold raw products (plain), natural-unit masked scores (packed mask path) or
+        // log2-unit scores (diagonal tiles, strided masks)
+        const float to_log2 = plain ? p.scale_log2 : ((MASKED && p.mask_vec) ? LOG2E : 1.f);
+        const uint64_t scale2 = am::pack2f(to_log2, to_log2);
         const uint64_t negm2 = am::pack2f(-m_safe, -m_safe);
         uint64_t lsum = am::pack2f(0.f, 0.f);
         auto exp32 = [&](const uint32_t (&r)[32], int c) {
@@ -606,15 +616,9 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
 #pragma unroll
           for (int i = 0; i < 32; i += 2) {
             const uint64_t xx = am::fma2(am::pack2u(r[i], r[i + 1]), scale2, negm2);
-            float p0, p1;
-            if (((i >> 1) & 3) < POLY_EXP_QUARTERS) {  // this share of the pairs runs on the FMA pipe
-              am::ex2_poly2(xx, p0, p1);
-            } else {
-              float x0, x1;
-              am::unpack2f(xx, x0, x1);
-              p0 = am::ex2(x0);
-              p1 = am::ex2(x1);
-            }
+            float x0, x1;
+            am::unpack2f(xx, x0, x1);
+            const float p0 = am::ex2(x0), p1 = am::ex2(x1);
             lsum = am::add2(lsum, am::pack2f(p0, p1));
             packed[i >> 1] = am::cvt_pair<T>(p0, p1);
           }
@@ -636,14 +640,10 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
         am::unpack2f(lsum, l0, l1);
         l += l0 + l1;
       }
-      PROF(4);
       ptx::tmem_st_wait();
       ptx::tc_fence_before();
       ptx::mbar_arrive(&p_full[t]);
-      PROF(5);
     }
-    if (threadIdx.x == 128) PROF_FLUSH(1);
-    if (threadIdx.x == 256) PROF_FLUSH(2);
     if (n > 0) {
       ptx::mbar_wait(&o_done[t], (n - 1) & 1, abort_flag, p.status, 33);
       ptx::tc_fence_after();
@@ -750,16 +750,20 @@ bool attn_tc_supported(const AttnArgs& a, int dtype, const void* q, const void* 
 template <typename T, int D, bool CAUSAL, bool MASKED>
 static int launch_fwd(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& mmask,
                       const FwdParams& p, cudaStream_t st) {
-  constexpr int SMEM = 6 * 128 * D * 2 + ((MASKED && D == 64) ? 2 * 128 * 128 * 2 : 0) + 1024 + 256;
+  constexpr int SMEM = 6 * 128 * D * 2 + ((MASKED && D == 64) ? 4 * 128 * 128 * 2 : 0) + 1024 + 256;
+  static_assert(SMEM <= 227 * 1024, "shared memory of one CTA");
   auto kern = attn_fwd_tc_kernel<T, D, CAUSAL, MASKED>;
-  static std::once_flag once;
-  static cudaError_t attr_err = cudaSuccess;
-  static int launch_regs = 0;
-  std::call_once(once, [&] {
-    attr_err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+  static std::atomic<unsigned long long> optin_done{0};
+  static std::atomic<int> launch_regs_cached{0};  // a property of the compiled code, the same on every device
+  cudaError_t attr_err = smem_optin_per_device(optin_done, reinterpret_cast<const void*>(kern), SMEM);
+  int launch_regs = launch_regs_cached.load(std::memory_order_relaxed);
+  if (attr_err == cudaSuccess && launch_regs == 0) {
     cudaFuncAttributes fa;
-    if (attr_err == cudaSuccess && (attr_err = cudaFuncGetAttributes(&fa, kern)) == cudaSuccess) launch_regs = fa.numRegs;
-  });
+    if ((attr_err = cudaFuncGetAttributes(&fa, kern)) == cudaSuccess) {
+      launch_regs = fa.numRegs;
+      launch_regs_cached.store(launch_regs, std::memory_order_relaxed);
+    }
+  }
   if (attr_err != cudaSuccess) {
     set_error("attention_fwd: cudaFuncSetAttribute failed: %s", cudaGetErrorString(attr_err));
     return (int)attr_err;
@@ -820,9 +824,3 @@ int launch_attn_fwd_tc(void* out, float* lse, const void* q, const void* k, cons
 }
 
 }  // namespace tb200
-
-#ifdef TB200_ATTN_PROFILE
-extern "C" int tb200_debug_read_prof_fwd(long long* out) {
-  return (int)cudaMemcpyFromSymbol(out, tb200::g_prof_fwd, sizeof(long long) * 64);
-}
-#endif

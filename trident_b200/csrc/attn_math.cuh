@@ -51,28 +51,6 @@ __device__ inline uint64_t mul2(uint64_t a, uint64_t b) {
   return d;
 }
 
-// 2^x for two values on the FMA pipe (no MUFU): x = j + f with j = round(x), f in [-0.5, 0.5];
-// 2^f from a degree-3 minimax polynomial (relative error 1.0e-4, below the rounding of a
-// 16-bit probability), and j added into the exponent field. x is clamped at -126; it must not
-// exceed about 100. Used for a fraction of the softmax exponentials so that the MUFU pipe
-// (16 results per clock per SM) and the FMA pipe share the work.
-__device__ inline void ex2_poly2(uint64_t x2, float& p0, float& p1) {
-  float x0, x1;
-  unpack2f(x2, x0, x1);
-  const uint64_t xc = pack2f(fmaxf(x0, -126.f), fmaxf(x1, -126.f));
-  const uint64_t xr = add2(xc, pack2f(12582912.f, 12582912.f));  // 1.5 * 2^23: integer part in the low bits
-  const uint64_t j = add2(xr, pack2f(-12582912.f, -12582912.f));
-  const uint64_t f = fma2(j, pack2f(-1.f, -1.f), xc);
-  uint64_t q = fma2(f, pack2f(0.05500893f, 0.05500893f), pack2f(0.24221096f, 0.24221096f));
-  q = fma2(q, f, pack2f(0.69328293f, 0.69328293f));
-  q = fma2(q, f, pack2f(1.f, 1.f));
-  float r0, r1, q0, q1;
-  unpack2f(xr, r0, r1);
-  unpack2f(q, q0, q1);
-  p0 = __int_as_float(__float_as_int(q0) + (__float_as_int(r0) << 23));
-  p1 = __int_as_float(__float_as_int(q1) + (__float_as_int(r1) << 23));
-}
-
 template <typename T>
 __device__ inline uint32_t cvt_pair(float a, float b);
 template <>

@@ -7,6 +7,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <atomic>
 #include <cstdarg>
 #include <cstdio>
 
@@ -21,7 +22,6 @@ void set_error(const char* fmt, ...);
 void note_kernel(const char* family, int launches);
 void add_launches(int launches);
 int sm_count();       // SMs of the current device (cached per device)
-bool force_simt();
 
 #define TB200_REQUIRE(cond, code, ...)     \
   do {                                     \
@@ -81,6 +81,22 @@ static inline cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 blo
   cfg.attrs = attr;
   cfg.numAttrs = cooperative ? 2 : 1;
   return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
+
+// Opt-in of a kernel to more than 48 KB of dynamic shared memory. The attribute belongs to the
+// (kernel, device) pair, so it is set once per device: `done` holds one bit per device ordinal
+// and lives beside the kernel (one static per template instantiation).
+static inline cudaError_t smem_optin_per_device(std::atomic<unsigned long long>& done, const void* kern, int bytes) {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess) {
+    cudaGetLastError();
+    dev = -1;
+  }
+  const bool tracked = dev >= 0 && dev < 64;
+  if (tracked && (done.load(std::memory_order_acquire) >> dev) & 1ull) return cudaSuccess;
+  const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  if (e == cudaSuccess && tracked) done.fetch_or(1ull << dev, std::memory_order_release);
+  return e;
 }
 
 static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }

@@ -399,11 +399,8 @@ template <typename T, bool AK, bool BK_, bool GEGLU>
 static int launch_variant(const TcGemmArgs& g, const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p,
                           cudaStream_t st) {
   auto kern = gemm_tc_kernel<T, AK, BK_, GEGLU>;
-  static std::once_flag once;
-  static cudaError_t attr_err = cudaSuccess;
-  std::call_once(once, [&] {
-    attr_err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
-  });
+  static std::atomic<unsigned long long> optin_done{0};
+  const cudaError_t attr_err = smem_optin_per_device(optin_done, reinterpret_cast<const void*>(kern), SMEM_BYTES);
   if (attr_err != cudaSuccess) {
     set_error("gemm_tc: cudaFuncSetAttribute failed: %s", cudaGetErrorString(attr_err));
     return (int)attr_err;

@@ -714,14 +714,18 @@ extern "C" int tb200_layer_norm_bwd_static(void* dx, void* dweight, void* dbias,
                                            const void* x, const void* weight, const float* mean,
                                            const float* rstd, int64_t rows, int64_t cols, int dtype,
                                            void* stream) {
-  TB200_REQUIRE(dx && dy && x && mean && rstd, TB200_ERR_INVALID,
-                "layer_norm_bwd_static: null pointer");
   TB200_REQUIRE(rows >= 0 && cols > 0, TB200_ERR_INVALID, "layer_norm_bwd_static: bad shape");
   TB200_REQUIRE(cols <= LN_STATIC_MAX_COLS, TB200_ERR_UNSUPPORTED,
                 "layer_norm_bwd_static: %lld columns exceed the built-in scratch (at most %lld); use "
                 "tb200_layer_norm_bwd with a workspace",
                 (long long)cols, (long long)LN_STATIC_MAX_COLS);
   cudaStream_t st = (cudaStream_t)stream;
+  if (rows == 0) {  // sums over no rows, exactly as tb200_layer_norm_bwd (data pointers may be null)
+    if (int rc = zero_fill(dweight, (size_t)cols * dtype_size(dtype), st, "layer_norm_bwd_static")) return rc;
+    return zero_fill(dbias, (size_t)cols * dtype_size(dtype), st, "layer_norm_bwd_static");
+  }
+  TB200_REQUIRE(dx && dy && x && mean && rstd, TB200_ERR_INVALID,
+                "layer_norm_bwd_static: null pointer");
   const bool want_cols = dweight || dbias;
   float* scratch = nullptr;
   if (want_cols) {
@@ -1133,7 +1137,9 @@ static GroupedPlan plan_grouped(int64_t cols, bool ptrs_ok, bool want_b) {
   return p;
 }
 
-static int g_norm_fused_finalize = 1;
+// Test hook of the calling thread (see tb200_set_norm_fused_finalize): thread-local, so one
+// thread's setting never changes another thread's dispatch.
+static thread_local int g_norm_fused_finalize = 1;
 
 // Launches the grouped kernel; returns the number of partial rows written (the grid size) in
 // *nparts. `grid_cap` bounds the grid (the workspace of the caller must hold that many rows).
@@ -1163,13 +1169,24 @@ static int launch_grouped(const GroupedPlan& gp, T* dx, float* partial, const T*
     }
     int cols_i = (int)cols, pc_i = (int)partial_cols, wc_i = want_cols ? 1 : 0, slab = 0;
     if (fuse && want_cols && g_norm_fused_finalize) {
-      // (the occupancy of one kernel instantiation depends on the shared-memory size only: cached)
+      // The occupancy of a kernel at a block size depends on the kernel, the shared-memory size
+      // and the device: the last answer is cached under all three (this lambda is shared by every
+      // instantiation with the same pointer type, so the kernel is part of the key).
+      static thread_local const void* cached_kern = nullptr;
       static thread_local size_t cached_smem = ~size_t(0);
+      static thread_local int cached_dev = -1;
       static thread_local int cached_per_sm = 0;
-      if (cached_smem != smem) {
+      int dev = -1;
+      if (cudaGetDevice(&dev) != cudaSuccess) {
+        (void)cudaGetLastError();
+        dev = -1;
+      }
+      if (cached_kern != (const void*)kern || cached_smem != smem || cached_dev != dev || dev < 0) {
         int q = 0;
         cached_per_sm = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&q, kern, 512, smem) == cudaSuccess ? q : 0;
+        cached_kern = (const void*)kern;
         cached_smem = smem;
+        cached_dev = dev;
       }
       const int per_sm = cached_per_sm;
       if ((int64_t)per_sm * sm_count() >= grid) {
