@@ -5,9 +5,12 @@
 
 One "step" is one forward + backward pass of a workload (a BASELINE configuration) over one
 batch of seeded synthetic input through the public functional API. Rank 0 prints ONE JSON
-line. With N > 1 (launched by torch.distributed.run, one rank per GPU) every rank runs its
-own shard of the workload; nothing is exchanged between ranks except the barrier and the
-max-over-ranks of the device time.
+line. With N > 1 (launched by torch.distributed.run, one rank per GPU) ONE configuration is split
+over the ranks (batch x head slices for attention, rows for the row operations and GEGLU; rank r
+of w owns blocks [8r/w, 8(r+1)/w) of 8), so the total work is fixed ("scaling": "strong") and
+`value` is the whole configuration's work over the slowest rank's device time. Nothing is
+exchanged between ranks except the barrier and the max-over-ranks of the device time. The former
+measurement, one full-size replica per rank, rides along under the key "weak".
 
   value     whole-job throughput with inputs resident in HBM; the step is replayed from a
             CUDA graph captured through the public API, timed with CUDA events
@@ -18,8 +21,11 @@ max-over-ranks of the device time.
   cpu_baseline  the torch eager CPU oracle on a bounded sample of the same workload
 
 `--impl reference` times the reference's CPU implementation of the path: the torch eager
-callables its tests use as oracle (the reference itself has no CPU kernels and its Triton
-kernels do not import under the installed Triton), on all host cores.
+callables its tests use as oracle (the reference itself has no CPU kernels), on all host cores,
+for the --steps / --warmup asked for, on a bounded sample of the same configuration.
+
+The last key of the line, "summary", repeats the main figures of every workload in a compact
+form (see "summary_keys").
 """
 
 import argparse
@@ -169,6 +175,17 @@ def reduce_sum(value, world, device):
     return float(t.item())
 
 
+def gather_all(value, world, device):
+    if world == 1:
+        return [value]
+    import torch.distributed as dist
+
+    t = torch.tensor([value], dtype=torch.float64, device=device)
+    out = [torch.zeros_like(t) for _ in range(world)]
+    dist.all_gather(out, t)
+    return [float(x.item()) for x in out]
+
+
 def barrier(world):
     if world > 1:
         import torch.distributed as dist
@@ -239,7 +256,8 @@ def time_device(wl, sets, steps, warmup, world, device):
     torch.cuda.synchronize()
     barrier(world)
     ms = start.elapsed_time(stop)
-    return reduce_max(ms, world, device) / 1e3, mode
+    per_rank = gather_all(ms, world, device)
+    return max(per_rank) / 1e3, mode, per_rank
 
 
 def time_e2e(wl, tensors, steps, warmup, world, device):
@@ -310,19 +328,19 @@ def time_e2e(wl, tensors, steps, warmup, world, device):
     return reduce_max(start.elapsed_time(stop), world, device) / 1e3, h2d, d2h
 
 
-# DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) of one full-size launch of each
-# workload's dominant kernel, from the ncu captures summarised under profiles/. A launch captured
-# on one of the 8 independent batches is scaled by 8 (the traffic grows in proportion). Bytes still in
-# L2 when the kernel ends are not in these figures.
-NCU_TRAFFIC = {
-    "softmax": (368.2e6, "profiles/softmax_bwd_vec_fp16_16384x4096.md"),
-    "masked_softmax": (367.5e6, "profiles/masked_softmax_vec_fp16_16384x4096.md"),
-    "layer_norm": (33.7e6, "profiles/norm_kernels_layer_norm_fp32_4096x1024_rms_norm_bf16_8192x4096.md"),
-    "rms_norm": (168.3e6, "profiles/norm_kernels_layer_norm_fp32_4096x1024_rms_norm_bf16_8192x4096.md"),
-    "attention_causal": (1305.2e6, "profiles/attn_tc_kernels_bf16_causal_S4096_D128.md (full-size capture)"),
-    "geglu": (1364.4e6, "profiles/gemm_tc_kernel_bf16_geglu_2048x4096x22016.md (full-size capture)"),
-    "attention_masked": (8 * 5139.2e6, "profiles/attn_tc_kernels_bf16_masked_S16384_D64.md (one of 8 batches, x8)"),
-}
+def ncu_traffic(name):
+    """DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) of one full-size launch of the
+    workload's dominant kernel, from the ncu capture recorded in profiles/traffic.json together with
+    the commit the capture was taken at. Bytes still in L2 when the kernel ends are not in it."""
+    path = os.path.join(ROOT, "profiles", "traffic.json")
+    try:
+        with open(path) as f:
+            rec = json.load(f).get(name)
+    except (OSError, ValueError):
+        rec = None
+    if not rec:
+        return None, "not captured"
+    return float(rec["bytes_per_launch"]), f"ncu capture of {rec['kernel']} at commit {rec['commit']} ({rec['scaled']})"
 
 
 def dominant_kernel(wl, tensors):
@@ -456,18 +474,33 @@ def cpu_run(wl, steps, warmup):
     return rate(wl, work, dt), cores, text, dt
 
 
+def config_of(wl, args):
+    """The `config` object of the JSON line: the same for this repo's arm and the reference arm
+    of one (workload, N) pair. What depends on the arm or on the run sits under "run"."""
+    n = args.gpus
+    return {
+        "workload": wl.describe + ("" if args.scale == 1 else f" [sharded dimension / {args.scale}]"),
+        "baseline_config": wl.config_index,
+        "l2": "inputs larger than 2x L2, or rotation over input sets whose total is (exact figures under 'run')",
+        "shard": ("one GPU, the whole configuration" if n == 1 else
+                  f"one configuration split over {n} ranks: blocks [8r/{n}, 8(r+1)/{n}) of 8 to rank r, no exchange"),
+    }
+
+
 def run_reference(args, wl):
     rank, _, world = dist_env()
     if rank != 0:
         return
-    steps = max(1, min(args.steps, 10))
-    warmup = max(1, min(args.warmup, 2))
+    steps, warmup = max(1, args.steps), max(0, args.warmup)
     value, cores, text, dt = cpu_run(wl, steps, warmup)
     line = {
         "impl": "reference", "metric": f"{wl.name} fwd+bwd {unit_of(wl)}", "value": value, "unit": unit_of(wl),
         "n_gpus": args.gpus, "steps": steps, "warmup": warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": str(wl.dtype).replace("torch.", ""), "data": "synthetic",
-        "config": {"workload": wl.describe, "baseline_config": wl.config_index, "sample": text},
+        "scaling": "strong" if args.gpus > 1 else "weak", "vs_baseline": None,
+        "dtype": str(wl.dtype).replace("torch.", ""), "data": "synthetic",
+        "config": config_of(wl, args),
+        "run": {"sample": text, "what": "torch eager on the host cores (the oracle the reference's tests use); "
+                                        "each step is one pass over the sample"},
         "cpu_baseline": {"value": value, "unit": unit_of(wl), "cores": cores, "kind": "port",
                          "sample": text + "; torch eager CPU (the oracle the reference's tests use)"},
         "e2e": {"value": value, "unit": unit_of(wl), "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -475,21 +508,26 @@ def run_reference(args, wl):
     emit(line)
 
 
+def input_sets(wl, tensors):
+    """Enough copies of the inputs that a rotation over them never finds a set in L2."""
+    nbytes = set_bytes(wl, tensors)
+    nsets = 1 if nbytes >= 2 * L2_BYTES else min(64, -(-3 * L2_BYTES // max(nbytes, 1)))
+    return [tensors] + [clone_set(tensors) for _ in range(nsets - 1)], nsets, nbytes
+
+
 def measure(wl, args, rank, world, device, with_cpu, sampler=None):
     from workloads import set_replica
 
     pk = peaks()
     kw = {"scale": args.scale} if args.scale > 1 else {}
-    set_replica(rank)  # weak scaling: every rank runs one full-size replica of the configuration
-    tensors = wl.make(0, 1, device, **kw)
+    set_replica(0)
+    tensors = wl.make(rank, world, device, **kw)  # this rank's shard of the one configuration
     work_local = wl.work(tensors)
-    nbytes = set_bytes(wl, tensors)
-    nsets = 1 if nbytes >= 2 * L2_BYTES else min(8, -(-3 * L2_BYTES // max(nbytes, 1)))
-    sets = [tensors] + [clone_set(tensors) for _ in range(nsets - 1)]
+    sets, nsets, nbytes = input_sets(wl, tensors)
     launches = launches_of_one_step(wl, tensors)
     if sampler:
         sampler.start()
-    secs, mode = time_device(wl, sets, args.steps, args.warmup, world, device)
+    secs, mode, per_rank_ms = time_device(wl, sets, args.steps, args.warmup, world, device)
     clocks = sampler.stop() if sampler else None
     work_total = reduce_sum(work_local, world, device)
     value = rate(wl, work_total * args.steps, secs)
@@ -497,22 +535,22 @@ def measure(wl, args, rank, world, device, with_cpu, sampler=None):
     label, kwork, ksecs, l2note = time_dominant(wl, sets, min(args.steps, 20), args.warmup)
     del sets[1:]
     achieved = rate(wl, kwork, ksecs)
-    traffic, traffic_src = NCU_TRAFFIC.get(wl.name, (None, "not captured"))
-    if args.scale != 1 and traffic is not None:
-        traffic = traffic / args.scale
+    traffic, traffic_src = ncu_traffic(wl.name)
+    if traffic is not None:
+        traffic = traffic / args.scale / world
     e2e_steps = max(3, min(args.steps, 20))
     esecs, h2d, d2h = time_e2e(wl, tensors, e2e_steps, 1, world, device)
     e2e_value = rate(wl, work_total * e2e_steps, esecs)
     out = {
         "metric": f"{wl.name} fwd+bwd {unit_of(wl)}", "value": value, "unit": unit_of(wl), "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": secs / args.steps * 1e3,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "higher_is_better": True, "scaling": "strong" if world > 1 else "weak", "vs_baseline": None,
         "dtype": str(wl.dtype).replace("torch.", ""), "data": "synthetic",
-        "config": {"workload": wl.describe + ("" if args.scale == 1 else f" [sharded dimension / {args.scale}]"),
-                   "baseline_config": wl.config_index, "launch": mode,
-                   "l2": (f"rotating {nsets} input sets ({nsets * nbytes / 2**20:.0f} MiB)" if nsets > 1
-                          else f"inputs {nbytes / 2**20:.0f} MiB exceed L2"),
-                   "shard": f"each of {world} rank(s) runs one full-size replica (replica = rank)"},
+        "config": config_of(wl, args),
+        "run": {"launch": mode,
+                "l2": (f"rotating {nsets} input sets ({nsets * nbytes / 2**20:.0f} MiB)" if nsets > 1
+                       else f"inputs {nbytes / 2**20:.0f} MiB exceed L2"),
+                "per_rank_ms_per_step": [round(m / args.steps, 5) for m in per_rank_ms]},
         "step_frac_of_peak": value / (peak * world),
         "roofline": {"bound": wl.bound, "kernel": label, "achieved": achieved, "peak": peak,
                      "unit": unit_of(wl), "frac": achieved / peak, "traffic": traffic,
@@ -524,6 +562,21 @@ def measure(wl, args, rank, world, device, with_cpu, sampler=None):
         "gpu_launches": launches * args.steps,
         "gpu_launches_per_step": launches,
     }
+    del tensors, sets
+    torch.cuda.empty_cache()
+    if world > 1:
+        # the earlier measurement: every rank runs a full-size replica of its own (per-GPU work fixed)
+        set_replica(rank)
+        full = wl.make(0, 1, device, **kw)
+        set_replica(0)
+        fsets, _, _ = input_sets(wl, full)
+        wsecs, _, wper = time_device(wl, fsets, args.steps, args.warmup, world, device)
+        wwork = reduce_sum(wl.work(full), world, device)
+        out["weak"] = {"value": rate(wl, wwork * args.steps, wsecs), "unit": unit_of(wl),
+                       "ms_per_step": wsecs / args.steps * 1e3,
+                       "what": f"each of {world} ranks runs one full-size replica (replica = rank)"}
+        del full, fsets
+        torch.cuda.empty_cache()
     if clocks is not None:
         out["clocks"] = clocks
     if with_cpu:
@@ -531,6 +584,18 @@ def measure(wl, args, rank, world, device, with_cpu, sampler=None):
         out["cpu_baseline"] = {"value": v, "unit": unit_of(wl), "cores": cores, "kind": "port",
                                "sample": text + "; torch eager CPU (the oracle the reference's tests use)"}
     return out
+
+
+SUMMARY_KEYS = ["value", "ms_per_step", "step_frac_of_peak", "roofline.frac", "e2e.value", "cpu_baseline.value"]
+
+
+def summary_row(m):
+    def sig(x):
+        return None if x is None else float(f"{x:.4g}")
+
+    return [sig(m.get("value")), sig(m.get("ms_per_step")), sig(m.get("step_frac_of_peak")),
+            sig(m.get("roofline", {}).get("frac")), sig(m.get("e2e", {}).get("value")),
+            sig(m.get("cpu_baseline", {}).get("value"))]
 
 
 def main():
@@ -543,8 +608,8 @@ def main():
     ap.add_argument("--scale", type=int, default=1,
                     help="divide the sharded dimension (rows, batch x heads) by this: small cases for profiling")
     ap.add_argument("--others", default="auto",
-                    help="comma list of further workloads reported under 'workloads' (auto: all at N=1, none "
-                         "otherwise; 'none' to skip)")
+                    help="comma list of further workloads reported under 'workloads' (auto: all of them; "
+                         "'none' to skip)")
     args = ap.parse_args()
 
     rank, local, world = dist_env()
@@ -577,22 +642,29 @@ def main():
     line = measure(wl, args, rank, world, device, with_cpu=(rank == 0 and world == 1), sampler=sampler)
     others = args.others
     if others == "auto":
-        others = ",".join(n for n in WORKLOADS if n != wl.name) if world == 1 else "none"
+        others = ",".join(n for n in WORKLOADS if n != wl.name)
     extra = {}
+    summary = {wl.name: summary_row(line)}
     if others != "none":
         for name in [n for n in others.split(",") if n]:
             try:
                 sub = measure(WORKLOADS[name], args, rank, world, device, with_cpu=(rank == 0 and world == 1))
                 extra[name] = {k: sub[k] for k in ("value", "unit", "ms_per_step", "step_frac_of_peak", "roofline",
-                                                   "e2e", "gpu_launches_per_step", "dtype") if k in sub}
+                                                   "e2e", "gpu_launches_per_step", "dtype", "run", "weak") if k in sub}
                 if "cpu_baseline" in sub:
                     extra[name]["cpu_baseline"] = sub["cpu_baseline"]
                 extra[name]["config"] = sub["config"]["workload"]
+                summary[name] = summary_row(sub)
             except Exception as exc:
                 extra[name] = {"error": repr(exc)}
+                if world > 1:
+                    raise  # a rank that left a collective half way would hang the others
             torch.cuda.empty_cache()
     if extra:
         line["workloads"] = extra
+    # last on the line, so that it survives a truncated record
+    line["summary_keys"] = SUMMARY_KEYS
+    line["summary"] = summary
     if rank == 0:
         emit(line)
     if world > 1:

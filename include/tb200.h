@@ -238,6 +238,13 @@ int tb200_device_status(int reset);
  * the calling thread and applies to the norm backward calls that thread makes; other threads
  * keep their own. Returns the old value. */
 int tb200_set_norm_fused_finalize(int on);
+/* Test hook of the calling thread for the bounded waits of the tensor-core kernels. mode 1: the
+ * attention forward launches this thread makes next run with a wait limit of about a
+ * millisecond and the producer of CTA (0, 0) leaves out the copy of its second key tile, so one
+ * wait runs out: the launch must still complete, free its tensor memory and leave a non-zero
+ * code in the device status word (tb200_device_status); its output is invalid. mode 0: normal
+ * operation. Returns the old mode. No memory is touched that a normal launch would not touch. */
+int tb200_test_wait_fault(int mode);
 
 #ifdef __cplusplus
 }

@@ -150,3 +150,32 @@ def test_attention_causal_full_config_properties(device):
     from trident_b200 import _lib
 
     assert _lib.device_status() == 0
+
+
+def test_attention_masked_full_config_properties(device):
+    """BASELINE.json config 4 at full size, [8,16,16384,64] with the [8,1,S,S] mask: everything
+    finite, no bounded wait expired, and one (batch, head) slice taken out of the full-size run
+    equals the same slice run alone (y, dk, dv bit for bit; dq up to its reduction order), which
+    in turn matches the CPU oracle."""
+    from trident_b200 import _lib
+
+    wl = WORKLOADS["attention_masked"]
+    t = wl.make(0, 1, device)
+    assert tuple(t["q"].shape) == (8, 16, 16384, 64) and tuple(t["mask"].shape) == (8, 1, 16384, 16384)
+    out = wl.step(t)
+    assert _lib.last_kernel() == "attn_tcgen05" and _lib.device_status() == 0
+    for name, v in out.items():
+        assert torch.isfinite(v.float()).all(), name
+    b, h = 5, 11
+    alone_in = {k: v[b:b + 1, h:h + 1].contiguous() for k, v in t.items() if k != "mask"}
+    alone_in["mask"] = t["mask"][b:b + 1]
+    alone = wl.step(alone_in)
+    for key in ("y", "dk", "dv"):
+        assert torch.equal(out[key][b:b + 1, h:h + 1], alone[key]), f"{key} of slice ({b},{h}) depends on the other slices"
+    util.assert_half_close(out["dq"][b:b + 1, h:h + 1], alone["dq"].float(), torch.bfloat16, atol=1e-3, ulps=1.0,
+                           what="dq of the slice, full run against alone")
+    del out, t
+    want = wl.run({k: v.float().cpu() for k, v in alone_in.items()}, torch_oracle)
+    for key in ("y", "dq", "dk", "dv"):
+        util.assert_half_close(alone[key], want[key], torch.bfloat16, atol=1e-2, ulps=1.0, what=f"slice {key}")
+    assert _lib.device_status() == 0

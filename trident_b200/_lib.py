@@ -29,6 +29,7 @@ SIGNATURES = {
     "tb200_last_kernel": (ctypes.c_char_p, []),
     "tb200_last_launch_count": (c_int, []),
     "tb200_set_norm_fused_finalize": (c_int, [c_int]),
+    "tb200_test_wait_fault": (c_int, [c_int]),
     "tb200_total_launches": (c_i64, []),
     "tb200_device_status": (c_int, [c_int]),
     "tb200_layer_norm_fwd": (c_int, [c_ptr] * 6 + [c_i64, c_i64, c_f32, c_int, c_ptr]),
@@ -112,6 +113,15 @@ def set_norm_fused_finalize(on):
     """Norm backward: fold the weight/bias gradient inside the main launch (default) or in a
     second kernel. Returns the old setting."""
     return load().tb200_set_norm_fused_finalize(1 if on else 0)
+
+
+def test_wait_fault(mode):
+    """Test hook (calling thread): 1 makes one bounded wait of the next attention forward launches
+    run out (see include/tb200.h); 0 restores normal operation. Returns the old mode."""
+    return load().tb200_test_wait_fault(int(mode))
+
+
+test_wait_fault.__test__ = False  # not a pytest test
 
 
 def dtype_code(dtype):

@@ -173,7 +173,7 @@ __global__ void __launch_bounds__(bwd_threads_for(D, MASKED), 1)
   uint64_t* dq_drained = bars + 10;  // dQ(s) read out            (128 arrivals)
   uint64_t* all_done = bars + 11;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
-  volatile uint32_t* abort_flag = tmem_slot + 1;
+  volatile uint32_t* abort_flag = tmem_slot + 1;  // [0] abort flag, [1] wait limit (ptx::mbar_wait)
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   int jt = blockIdx.x;
@@ -205,9 +205,10 @@ __global__ void __launch_bounds__(bwd_threads_for(D, MASKED), 1)
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < 12; ++i) ptx::mbar_init(&bars[i], (i == 6 || i == 8) ? COMPUTE_WARPS * 32 : (i == 10 ? 128 : 1));
-    *abort_flag = 0;
+    abort_flag[0] = 0;
+    abort_flag[1] = ptx::WAIT_LIMIT_UNITS;
     if ((ptx::smem_u32(smem) & 1023u) != 0) {  // swizzled tiles need a 1024-byte aligned base
-      *abort_flag = 1;
+      abort_flag[0] = 1;
       atomicCAS(p.status, 0, 40);
     }
     ptx::fence_barrier_init();
@@ -255,6 +256,11 @@ __global__ void __launch_bounds__(bwd_threads_for(D, MASKED), 1)
       bulk_load(nlse_smem + st * 128, p.nlse2 + row0, 512, &qdo_full[st]);
       bulk_load(ndelta_smem + st * 128, p.ndelta + row0, 512, &qdo_full[st]);
     }
+    // Drain: every copy issued above has landed before the CTA gives up its shared memory (on the
+    // normal path the consumers have waited for all of them already).
+    ptx::mbar_wait_drain(kv_full, 0, abort_flag, p.status, 54);
+    for (int s = steps > 2 ? steps - 2 : 0; s < steps; ++s)
+      ptx::mbar_wait_drain(&qdo_full[s & 1], (s >> 1) & 1, abort_flag, p.status, 54);
   } else if (warp == 1 && lane == 0) {
     // ---------------------------------------------------------------- MMA issuer
     const uint32_t ka = ptx::smem_u32(k_smem), va = ptx::smem_u32(v_smem);
@@ -324,6 +330,10 @@ __global__ void __launch_bounds__(bwd_threads_for(D, MASKED), 1)
       ptx::umma_commit(dq_ready);
     }
     ptx::umma_commit(all_done);
+    // Tensor memory is freed after the CTA-wide barrier at the end: the issuer itself waits until
+    // everything it issued has completed (the compute warps wait for the same barrier, but after
+    // an aborted wait they may pass it early).
+    ptx::mbar_wait_drain(all_done, 0, abort_flag, p.status, 53);
   } else if (warp >= 4 && warp < DRAIN_WARP0) {
     // ---------------------------------------------------------------- P^T / dS^T (lane = key row)
     // warps 4-7 take the first 128 / CGROUPS query columns of their rows, warps 8-11 the next, ...

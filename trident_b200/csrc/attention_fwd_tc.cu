@@ -65,6 +65,8 @@ struct FwdParams {
   int* status;
   float scale_log2;   // softmax scale * log2(e)
   int nq;             // query tiles per (batch, head)
+  uint32_t wait_units;  // limit of every bounded wait, in units of 65536 cycles
+  int skip_k_tile;      // -1; a test sets the key tile whose copy CTA (0, 0) leaves out
 };
 
 template <typename T>
@@ -179,8 +181,9 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
   uint64_t* s_free = bars + 16;      // [2]  softmax -> MMA: scores read into registers (P_SPLIT)
   uint64_t* mask_full = bars + 18;   // [2 tiles][2 stages]  mask producer -> softmax of query tile t
   uint64_t* mask_empty = bars + 22;  // [2 tiles][2 stages]  softmax -> mask producer: last read done
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 26);
-  volatile uint32_t* abort_flag = tmem_slot + 1;
+  uint64_t* mma_drained = bars + 26; // MMA issuer: every product it issued has completed
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 27);
+  volatile uint32_t* abort_flag = tmem_slot + 1;  // [0] abort flag, [1] wait limit (ptx::mbar_wait)
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // CTAs are numbered x-fastest. With a mask that is broadcast over heads the head index is
@@ -214,7 +217,9 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
     }
     ptx::mbar_init(&s_free[0], 128);
     ptx::mbar_init(&s_free[1], 128);
-    *abort_flag = 0;
+    ptx::mbar_init(mma_drained, 1);
+    abort_flag[0] = 0;
+    abort_flag[1] = p.wait_units;
     ptx::fence_barrier_init();
     ptx::prefetch_tensormap(&map_q);
     ptx::prefetch_tensormap(&map_k);
@@ -255,15 +260,26 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
       const int st = j & 1;
       const uint32_t ph = (j >> 1) & 1;
       ptx::mbar_wait(&k_empty[st], ph ^ 1, abort_flag, p.status, 11);
-      ptx::mbar_expect_tx(&k_full[st], TILE_BYTES);
+      if (!(j == p.skip_k_tile && blockIdx.x == 0 && blockIdx.y == 0)) {  // (test hook: see FwdParams)
+        ptx::mbar_expect_tx(&k_full[st], TILE_BYTES);
 #pragma unroll
-      for (int c = 0; c < NBOX; ++c)
-        tma_load_4d(k_smem + st * TILE_BYTES + c * BOX_BYTES, &map_k, &k_full[st], c * 64, j * TK, h, b);
+        for (int c = 0; c < NBOX; ++c)
+          tma_load_4d(k_smem + st * TILE_BYTES + c * BOX_BYTES, &map_k, &k_full[st], c * 64, j * TK, h, b);
+      }
       ptx::mbar_wait(&v_empty[st], ph ^ 1, abort_flag, p.status, 12);
       ptx::mbar_expect_tx(&v_full[st], TILE_BYTES);
 #pragma unroll
       for (int c = 0; c < NBOX; ++c)
         tma_load_4d(v_smem + st * TILE_BYTES + c * BOX_BYTES, &map_v, &v_full[st], c * 64, j * TK, h, b);
+    }
+    // Drain: the CTA's shared memory is given up when the CTA ends, so every copy issued above
+    // must have landed by then. On the normal path the MMA issuer has consumed them all; after an
+    // aborted wait it may have run ahead, so the last copy into each stage is waited for here.
+    ptx::mbar_wait_drain(&q_full[0], 0, abort_flag, p.status, 15);
+    if (active1) ptx::mbar_wait_drain(&q_full[1], 0, abort_flag, p.status, 15);
+    for (int j = nmax > 2 ? nmax - 2 : 0; j < nmax; ++j) {
+      ptx::mbar_wait_drain(&k_full[j & 1], (j >> 1) & 1, abort_flag, p.status, 16);
+      ptx::mbar_wait_drain(&v_full[j & 1], (j >> 1) & 1, abort_flag, p.status, 17);
     }
   } else if (MASK_SMEM && warp == 3 && lane == 0) {
     // ---------------------------------------------------------------- mask producer
@@ -291,6 +307,13 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
                           p.mask_has_h ? h : 0, p.mask_has_b ? b : 0);
           }
         }
+      }
+      // drain (see the K/V producer): the last copy into each stage has landed
+#pragma unroll
+      for (int t = 0; t < 2; ++t) {
+        const int nt = t == 0 ? n0 : n1;
+        for (int j = nt > 2 ? nt - 2 : 0; j < nt; ++j)
+          ptx::mbar_wait_drain(&mask_full[t * 2 + (j & 1)], (j >> 1) & 1, abort_flag, p.status, 18);
       }
     }
   } else if (warp == 1) {
@@ -404,6 +427,12 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
       }
     }
     }
+    // Tensor memory is freed after the CTA-wide barrier at the end. On the normal path the softmax
+    // warps have waited for the last product; after an aborted wait they may not have, so the
+    // issuer itself waits until everything it issued has completed.
+    commit_(mma_drained);
+    if (elected) ptx::mbar_wait_drain(mma_drained, 0, abort_flag, p.status, 19);
+    __syncwarp();
   }
   } else {
     // ---------------------------------------------------------------- softmax + epilogue
@@ -796,6 +825,9 @@ int launch_attn_fwd_tc(void* out, float* lse, const void* q, const void* k, cons
   p.status = device_status_ptr();
   p.scale_log2 = a.scale * LOG2E;
   p.nq = (int)(a.S / TQ);
+  const bool fault_test = test_wait_fault_mode() == 1;
+  p.wait_units = fault_test ? 30u : ptx::WAIT_LIMIT_UNITS;  // 30 x 65536 cycles: about a millisecond
+  p.skip_k_tile = fault_test ? 1 : -1;
   CUtensorMap mmask = mq;  // placeholder when no mask tile is staged
   p.mask_tma = 0;
   p.mask_has_b = mask && a.ms[0] != 0;

@@ -38,6 +38,9 @@ int* device_status_ptr() {
   return p;
 }
 
+static thread_local int g_test_wait_fault = 0;
+int test_wait_fault_mode() { return g_test_wait_fault; }
+
 namespace {
 
 constexpr int BM = 128, BN = 256, BK = 64, STAGES = 4;
@@ -122,8 +125,9 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
   uint64_t* empty_bar = bars + STAGES;       // [STAGES]  MMA -> TMA
   uint64_t* acc_full = bars + 2 * STAGES;    // [2]       MMA -> epilogue
   uint64_t* acc_empty = bars + 2 * STAGES + 2;  // [2]    epilogue -> MMA
-  uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
-  volatile uint32_t* abort_flag = tmem_base_slot + 1;
+  uint64_t* mma_drained = bars + 2 * STAGES + 4;  // MMA issuer: every product it issued has completed
+  uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 5);
+  volatile uint32_t* abort_flag = tmem_base_slot + 1;  // [0] abort flag, [1] wait limit (ptx::mbar_wait)
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int num_tiles = p.num_m_tiles * p.num_n_tiles;
@@ -137,7 +141,9 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
       ptx::mbar_init(&acc_full[s], 1);
       ptx::mbar_init(&acc_empty[s], 4);
     }
-    *abort_flag = 0;
+    ptx::mbar_init(mma_drained, 1);
+    abort_flag[0] = 0;
+    abort_flag[1] = ptx::WAIT_LIMIT_UNITS;
     ptx::fence_barrier_init();
     ptx::prefetch_tensormap(&map_a);
     ptx::prefetch_tensormap(&map_b);
@@ -224,6 +230,11 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
         acc_phase ^= 1;
       }
     }
+    // Tensor memory is freed after the CTA-wide barrier below. On the normal path the epilogue has
+    // waited for every accumulator; after an aborted wait it may not have, so the issuer itself
+    // waits until the products it issued have completed.
+    ptx::umma_commit(mma_drained);
+    ptx::mbar_wait_drain(mma_drained, 0, abort_flag, p.status, 5);
   } else if (warp >= 4) {
     // ------------------------------------------------------------ epilogue
     const int quarter = warp & 3;  // tensor-memory lanes [32*quarter, 32*quarter+32)
@@ -473,4 +484,16 @@ extern "C" int tb200_device_status(int reset) {
     cudaMemcpyToSymbol(tb200::g_device_status, &zero, sizeof(int));
   }
   return v;
+}
+
+// Test hook of the calling thread. mode 1: the next attention forward launches of this thread run
+// with a wait limit of about one millisecond, and the producer of CTA (0, 0) leaves out the bulk
+// copy of its second key tile (it touches no memory it would not otherwise touch), so that the
+// MMA issuer's wait for that tile runs out: the kernel must still end, free its tensor memory
+// and leave a non-zero code in the device status word. mode 0: normal operation. Returns the
+// old mode.
+extern "C" int tb200_test_wait_fault(int mode) {
+  const int old = tb200::g_test_wait_fault;
+  tb200::g_test_wait_fault = mode;
+  return old;
 }

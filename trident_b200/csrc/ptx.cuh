@@ -47,12 +47,14 @@ __device__ inline bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 
-// Every wait in the tensor-core kernels is bounded: after WAIT_LIMIT clock cycles the
-// waiting thread raises the CTA's abort flag (shared memory) and records `code` in the
-// library's device status word. Once the flag is up every later wait of the CTA returns
-// after at most 1024 polls, so the kernel runs to its normal end (releasing tensor memory)
-// with an invalid result instead of hanging.
-constexpr long long WAIT_LIMIT = 4000000000LL;  // about two seconds of SM clock
+// Every wait in the tensor-core kernels is bounded. `abort_flag` points at two words of the
+// CTA's shared memory: [0] the abort flag, [1] the wait limit in units of 65536 clock cycles
+// (set by the kernel from its parameters; WAIT_LIMIT_UNITS unless a test shortens it). After
+// that many cycles the waiting thread raises the abort flag and records `code` in the library's
+// device status word. Once the flag is up every later wait of the CTA returns after at most
+// 1024 polls, so the kernel runs to its normal end (its roles then drain what they have in
+// flight and tensor memory is released) with an invalid result instead of hanging.
+constexpr uint32_t WAIT_LIMIT_UNITS = 61035;  // x 65536 cycles: about two seconds of SM clock
 
 __device__ inline void mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag,
                                  int* status, int code) {
@@ -61,12 +63,29 @@ __device__ inline void mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32
   uint32_t polls = 0;
   while (!mbar_try_wait(bar, parity)) {
     if ((++polls & 1023u) == 0) {
-      if (*abort_flag) return;
-      if (clock64() - start > WAIT_LIMIT) {
-        *abort_flag = 1;
+      if (abort_flag[0]) return;
+      if (clock64() - start > (static_cast<long long>(abort_flag[1]) << 16)) {
+        abort_flag[0] = 1;
         if (status) atomicCAS(status, 0, code);
         return;
       }
+    }
+  }
+}
+// The same wait for a role's last act, draining what it put in flight (bulk copies into the
+// CTA's shared memory, tcgen05.mma writing tensor memory) before the CTA releases both: it
+// does not return early when the abort flag is up, only when the barrier completes or the
+// time limit passes.
+__device__ inline void mbar_wait_drain(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag,
+                                       int* status, int code) {
+  if (mbar_try_wait(bar, parity)) return;
+  const long long start = clock64();
+  uint32_t polls = 0;
+  while (!mbar_try_wait(bar, parity)) {
+    if ((++polls & 1023u) == 0 && clock64() - start > (static_cast<long long>(abort_flag[1]) << 16)) {
+      abort_flag[0] = 1;
+      if (status) atomicCAS(status, 0, code);
+      return;
     }
   }
 }
@@ -234,5 +253,7 @@ bool make_tensor_map_3d(CUtensorMap* map, const void* base, uint64_t batch, uint
 
 // Device status word of the tensor-core kernels (0 = no bounded wait has ever expired).
 int* device_status_ptr();
+// Test hook of the calling thread (tb200_test_wait_fault): 0 = normal operation.
+int test_wait_fault_mode();
 
 }  // namespace tb200
