@@ -487,11 +487,77 @@ def config_of(wl, args):
     }
 
 
+# Bounded samples for the reference's own Triton kernels (its attention backward runs one
+# program of two warps per (batch, head): 0.25 s per slice at S = 4096).
+TRITON_SAMPLE = {
+    "attention_causal": ({"scale": 64}, "2 of 128 (batch, head) slices"),
+    "attention_masked": ({"scale": 16, "_world": 8}, "1 of 128 (batch, head) slices, one mask slab"),
+    "geglu": ({"scale": 4}, "2048 of 8192 rows, full weight"),
+}
+REF_DIR = os.path.join(ROOT, "baseline", "_ref")
+
+
+def triton_reference_run(wl, steps, warmup, local):
+    """The reference's own kernels (the patched copy under baseline/_ref) on this GPU."""
+    if not torch.cuda.is_available():
+        raise RuntimeError("no CUDA device")
+    if not os.path.isdir(os.path.join(REF_DIR, "trident")):
+        raise RuntimeError("baseline/_ref is absent (python baseline/make_ref.py builds it)")
+    sys.path.insert(0, REF_DIR)
+    try:
+        import trident as reference
+    finally:
+        sys.path.remove(REF_DIR)
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    kw, text = TRITON_SAMPLE.get(wl.name, ({}, "full configuration"))
+    kw = dict(kw)
+    world = kw.pop("_world", 1)
+    tensors = wl.make(0, world, device, **kw)
+    work = wl.work(tensors)
+    for _ in range(max(warmup, 1)):  # the first call autotunes and compiles
+        wl.run(tensors, reference.function)
+    torch.cuda.synchronize()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(steps):
+        wl.run(tensors, reference.function)
+    stop.record()
+    torch.cuda.synchronize()
+    dt = start.elapsed_time(stop) / 1e3 / steps
+    return rate(wl, work, dt), text, dt
+
+
 def run_reference(args, wl):
-    rank, _, world = dist_env()
+    rank, local, world = dist_env()
     if rank != 0:
         return
     steps, warmup = max(1, args.steps), max(0, args.warmup)
+    kind, why_cpu = "cpu", None
+    if args.reference_kind in ("auto", "triton"):
+        try:
+            value, text, dt = triton_reference_run(wl, steps, warmup, local)
+            kind = "triton"
+        except Exception as exc:  # no GPU here, no copy, or the copy fails under this Triton
+            why_cpu = f"{type(exc).__name__}: {exc}"[:300]
+            if args.reference_kind == "triton":
+                emit({"impl": "reference", "unavailable": f"the reference's Triton kernels did not run: {why_cpu}"})
+                return
+    if kind == "triton":
+        emit({
+            "impl": "reference", "reference_kind": "triton", "metric": f"{wl.name} fwd+bwd {unit_of(wl)}",
+            "value": value, "unit": unit_of(wl), "n_gpus": args.gpus, "steps": steps, "warmup": warmup,
+            "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "strong" if args.gpus > 1 else "weak",
+            "vs_baseline": None, "dtype": str(wl.dtype).replace("torch.", ""), "data": "synthetic",
+            "config": config_of(wl, args),
+            "run": {"sample": text, "what": "the reference's own Triton kernels (copy patched for the installed "
+                                            "Triton's API, autotuning on) through trident.function on one GPU; "
+                                            "each step is one forward + backward over the sample"},
+            "cpu_baseline": {"value": value, "unit": unit_of(wl), "cores": 0, "kind": "reference",
+                             "sample": text + "; the reference's own kernels on the same GPU (not a CPU run)"},
+            "e2e": {"value": value, "unit": unit_of(wl), "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        })
+        return
     value, cores, text, dt = cpu_run(wl, steps, warmup)
     line = {
         "impl": "reference", "metric": f"{wl.name} fwd+bwd {unit_of(wl)}", "value": value, "unit": unit_of(wl),
@@ -499,8 +565,10 @@ def run_reference(args, wl):
         "scaling": "strong" if args.gpus > 1 else "weak", "vs_baseline": None,
         "dtype": str(wl.dtype).replace("torch.", ""), "data": "synthetic",
         "config": config_of(wl, args),
+        "reference_kind": "cpu",
         "run": {"sample": text, "what": "torch eager on the host cores (the oracle the reference's tests use); "
-                                        "each step is one pass over the sample"},
+                                        "each step is one pass over the sample",
+                "why_not_triton": why_cpu},
         "cpu_baseline": {"value": value, "unit": unit_of(wl), "cores": cores, "kind": "port",
                          "sample": text + "; torch eager CPU (the oracle the reference's tests use)"},
         "e2e": {"value": value, "unit": unit_of(wl), "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -604,6 +672,9 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--reference-kind", default="auto", choices=["auto", "triton", "cpu"],
+                    help="--impl reference: the reference's own Triton kernels on the GPU (a patched copy under "
+                         "baseline/_ref; 'auto' takes them when they run) or torch eager on the host cores")
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD)
     ap.add_argument("--scale", type=int, default=1,
                     help="divide the sharded dimension (rows, batch x heads) by this: small cases for profiling")
