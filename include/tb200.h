@@ -85,7 +85,8 @@ int tb200_layer_norm_bwd_static(void* dx, void* dweight /*nullable*/, void* dbia
  * Replaces kernel.RMSNorm.forward (trident/kernel/rms_norm.py:19-117), launched at
  * trident/operation/rms_norm.py:60. rms = sqrt(mean(x[:partial_cols]^2));
  * y = x / (rms + eps) * weight (+ bias). x is addressed with (row_stride,
- * col_stride); y is contiguous. */
+ * col_stride); y is contiguous. y may be null: then only rms is written (the row
+ * statistic for tb200_geglu_fwd_row_scaled). */
 int tb200_rms_norm_fwd(void* y, float* rms, const void* x, const void* weight,
                        const void* bias /*nullable*/, int64_t rows, int64_t cols,
                        int64_t row_stride, int64_t col_stride, int64_t partial_cols,
@@ -158,6 +159,17 @@ int tb200_geglu_fwd(void* out, void* state_gate, const void* x, const void* w,
                     const void* bias /*nullable*/, int64_t B, int64_t M, int64_t N, int64_t K,
                     int64_t x_sb, int64_t x_sm, int64_t x_sk, int64_t w_sn, int64_t w_sk,
                     int gelu_tanh, int allow_tf32, int dtype, void* stream);
+/* The same with every accumulator row m multiplied by row_scale[m] (fp32, [B*M]) before the bias:
+ * state_gate = row_scale * (x w^T) + bias. Given row_scale = 1 / (rms + eps) (tb200_rms_norm_fwd
+ * with y = null returns rms alone) and w = W * diag(norm weight), this is GEGLU applied to
+ * RMSNorm(x), the two reference launches trident/function/function.py:202-208 and :70-80 that run
+ * back to back, without the normalised copy of x going through memory. 16-bit operands with unit
+ * inner strides only; anything else returns TB200_ERR_UNSUPPORTED and the caller runs the two
+ * operations one after the other. */
+int tb200_geglu_fwd_row_scaled(void* out, void* state_gate, const void* x, const void* w,
+                               const void* bias /*nullable*/, const float* row_scale, int64_t B, int64_t M,
+                               int64_t N, int64_t K, int64_t x_sb, int64_t x_sm, int64_t x_sk,
+                               int64_t w_sn, int64_t w_sk, int gelu_tanh, int dtype, void* stream);
 /* d_state_gate[:, :N/2] = dout * gelu(gate); d_state_gate[:, N/2:] = dout * state *
  * gelu'(gate). Replaces kernel.GEGLU.backward (trident/kernel/geglu.py:179-242;
  * launched at trident/operation/geglu.py:101). */

@@ -169,11 +169,117 @@ def test_argument_errors(device):
     with pytest.raises(ValueError):
         f(q[0], q[0], q[0])
     with pytest.raises(ValueError):
-        f(q[:, :, :6], q[:, :, :6], q[:, :, :6])
+        f(q[..., :6], q[..., :6], q[..., :6])  # the head size must be a power of two
     with pytest.raises(ValueError):
         f(q, q, q, attn_mask=torch.zeros(1, 1, 8, 8, device=device), is_causal=True)
     with pytest.raises(ValueError):
-        f(q, q, q, attn_mask=torch.zeros(1, 1, 8, 8, device=device, dtype=torch.bool))
+        f(q, q, q, dropout_p=1.5)
+
+
+@pytest.mark.parametrize("dt, S, D", [(torch.float32, 100, 32), (torch.bfloat16, 256, 64), (torch.bfloat16, 200, 128)])
+@pytest.mark.parametrize("mask_shape", ["bhss", "b1ss", "11ss", "b11s"])
+def test_boolean_mask(dt, S, D, mask_shape, device):
+    """A boolean mask means True = attend, as in the torch oracle."""
+    B, H = 2, 2
+    q, k, v, dy = (util.randn(B, H, S, D, seed=s, dtype=dt) for s in (1, 2, 3, 5))
+    shape = {"bhss": (B, H, S, S), "b1ss": (B, 1, S, S), "11ss": (1, 1, S, S), "b11s": (B, 1, 1, S)}[mask_shape]
+    mask = util.rand(*shape, seed=6) < 0.8
+    mask[..., 0] = True
+
+    def train(fn, dev, up):
+        i, j, l = (t.detach().clone().to(dev).to(up).requires_grad_(True) for t in (q, k, v))
+        y = fn(i, j, l, attn_mask=mask.to(dev))
+        y.backward(dy.to(dev).to(up))
+        return y, i.grad, j.grad, l.grad
+
+    got = train(trident.function.scaled_dot_product_attention, device, dt)
+    want = train(torch_oracle.scaled_dot_product_attention, "cpu", torch.float32)
+    for g, w_, name in zip(got, want, ["y", "dq", "dk", "dv"]):
+        if dt == torch.float32:
+            util.assert_close(g, w_, 1e-5, 2e-4, f"bool mask {name}")
+        else:
+            util.assert_half_close(g, w_, dt, atol=1e-2, ulps=1.0, what=f"bool mask {name}")
+
+
+@pytest.mark.parametrize(
+    "dt, S, D, mode",
+    [
+        (torch.float32, 100, 32, "causal"),
+        (torch.float32, 300, 64, "mask"),
+        (torch.bfloat16, 100, 64, "none"),
+        (torch.bfloat16, 200, 64, "causal"),
+        (torch.bfloat16, 200, 64, "none"),
+        (torch.bfloat16, 1000, 128, "causal"),
+        (torch.bfloat16, 600, 128, "none"),
+        (torch.bfloat16, 333, 64, "mask"),
+        (torch.bfloat16, 333, 128, "mask_b11s"),
+        (torch.float16, 130, 64, "mask"),
+    ],
+)
+def test_any_sequence_length(dt, S, D, mode, device):
+    """Sequence lengths that are not powers of two (16-bit lengths above one tile that are not a
+    multiple of it are zero-padded onto the tensor-core kernels)."""
+    B, H = 2, 2
+    q, k, v, dy = (util.randn(B, H, S, D, seed=s, dtype=dt) for s in (1, 2, 3, 5))
+    mask = None
+    if mode.startswith("mask"):
+        shape = (B, 1, 1, S) if mode == "mask_b11s" else (B, H, S, S)
+        mask = util.randn(*shape, seed=4)
+        drop = util.rand(*shape, seed=6) < 0.2
+        drop[..., 0] = False
+        mask = mask.masked_fill(drop, float("-inf")).to(dt)
+
+    def train(fn, dev, up):
+        i, j, l = (t.detach().clone().to(dev).to(up).requires_grad_(True) for t in (q, k, v))
+        m = None if mask is None else mask.to(dev).to(up).requires_grad_(True)
+        y = fn(i, j, l, attn_mask=m, is_causal=(mode == "causal"))
+        y.backward(dy.to(dev).to(up))
+        return [y, i.grad, j.grad, l.grad] + ([] if m is None else [m.grad])
+
+    got = train(trident.function.scaled_dot_product_attention, device, dt)
+    want = train(torch_oracle.scaled_dot_product_attention, "cpu", torch.float32)
+    for g, w_, name in zip(got, want, ["y", "dq", "dk", "dv", "dmask"]):
+        assert g.shape == w_.shape, name
+        if dt == torch.float32:
+            util.assert_close(g, w_, 1e-5, 5e-4, f"S={S} {name}")
+        elif name == "dmask":
+            # the dense 16-bit gradient is summed over the mask's broadcast dimensions (heads, query
+            # rows): its rounding errors add up, so the sum is held to a relative bound
+            rel = (g.float().cpu() - w_).norm() / w_.norm()
+            assert rel < 2.0 ** -7, f"S={S} {mode} dmask: relative error {rel:.3e}"
+        else:
+            util.assert_half_close(g, w_, dt, atol=1e-2, ulps=1.0, what=f"S={S} {mode} {name}")
+    if dt != torch.float32 and S > 128:
+        from trident_b200 import _lib
+
+        if mask is None:
+            assert _lib.last_kernel() == "attn_tcgen05"
+
+
+@pytest.mark.parametrize("dt, S, D", [(torch.float32, 64, 32), (torch.bfloat16, 256, 64)])
+def test_output_dropout(dt, S, D, device):
+    """dropout_p > 0 drops elements of the attention output (scaled by 1 / (1 - p)) and the
+    gradient follows the same mask."""
+    B, H, p = 2, 4, 0.25
+    q, k, v, dy = (util.randn(B, H, S, D, seed=s, dtype=dt, device=device) for s in (1, 2, 3, 5))
+    f = trident.function.scaled_dot_product_attention
+    base = f(q, k, v, is_causal=True)
+    i, j, l = (t.detach().clone().requires_grad_(True) for t in (q, k, v))
+    torch.manual_seed(7)
+    y = f(i, j, l, dropout_p=p, is_causal=True)
+    kept = y != 0
+    frac = 1.0 - kept.float().mean().item()
+    assert abs(frac - p) < 0.02, frac
+    scaled = (base.float() / (1.0 - p)).to(dt)
+    assert torch.allclose(y[kept].float(), scaled[kept].float(), rtol=2.0 ** -7 if dt != torch.float32 else 1e-6, atol=1e-6)
+    y.backward(dy)
+    # the same gradients as the dropout-free op fed with the masked, rescaled gradient
+    a, b, c = (t.detach().clone().requires_grad_(True) for t in (q, k, v))
+    f(a, b, c, is_causal=True).backward((dy.float() * kept / (1.0 - p)).to(dt))
+    for g, w_, name in zip((i.grad, j.grad, l.grad), (a.grad, b.grad, c.grad), ("dq", "dk", "dv")):
+        assert torch.allclose(g.float(), w_.float(), rtol=1e-2, atol=2e-3), name
+    m = trident.ScaledDotProductAttention(dropout_p=p, is_causal=True).eval()
+    assert torch.equal(m(q, k, v), base)
 
 
 @pytest.mark.parametrize(

@@ -67,13 +67,13 @@ def test_attention_argument_errors_before_any_launch():
     with pytest.raises(ValueError, match="dimension"):
         f(q[0], q[0], q[0])
     with pytest.raises(ValueError, match="power of 2"):
-        f(q[:, :, :6], q[:, :, :6], q[:, :, :6])
+        f(q[..., :6], q[..., :6], q[..., :6])  # head size
     with pytest.raises(ValueError, match="both attn_mask and is_causal"):
         f(q, q, q, attn_mask=torch.zeros(1, 1, 8, 8), is_causal=True)
-    with pytest.raises(ValueError, match="Boolean mask"):
-        f(q, q, q, attn_mask=torch.zeros(1, 1, 8, 8, dtype=torch.bool))
     with pytest.raises(ValueError, match="dropout"):
-        f(q, q, q, dropout_p=0.1)
+        f(q, q, q, dropout_p=1.0)
+    with pytest.raises(ValueError, match="same shape"):
+        f(q, q[:, :, :4], q)
 
 
 def test_no_cpu_fallback():

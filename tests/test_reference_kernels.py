@@ -11,6 +11,12 @@ bound is asked of |ours - reference's|.
 
 Attention is only run at sequence lengths of at least the reference's largest tile (64): below
 that its kernel loads whole tiles without a bounds check (trident/kernel/attention.py:115,140,148).
+
+The reference autotunes every kernel per shape, which takes minutes for its GEMMs (about three
+per Linear / GEGLU shape) and half a minute per attention shape. By default the quick cases run
+(the row operations and the reference's own attention test shape, about a minute); setting the
+environment variable TB200_REFERENCE_FULL=1 adds Linear, GEGLU and the other attention shapes
+(about eight minutes).
 """
 
 import os
@@ -22,6 +28,9 @@ import torch
 import trident_b200 as ours
 
 pytestmark = pytest.mark.gpu
+
+FULL = os.environ.get("TB200_REFERENCE_FULL", "0") == "1"
+slow = pytest.mark.skipif(not FULL, reason="minutes of reference autotuning: set TB200_REFERENCE_FULL=1")
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 REF_DIR = os.path.join(ROOT, "baseline", "_ref")
@@ -86,6 +95,7 @@ def test_rms_norm(ref, rows, cols, p, device):
     _compare(got, want, 1e-2, "rms_norm")
 
 
+@slow
 @pytest.mark.parametrize("B, M, N, K", [(2, 16, 32, 128), (2, 512, 512, 100)])
 def test_linear_and_geglu(ref, B, M, N, K, device):
     x, w, b = _randn(B, M, K, seed=1, device=device), _randn(N, K, seed=2, device=device), _randn(N, seed=3, device=device)
@@ -106,7 +116,11 @@ def test_linear_and_geglu(ref, B, M, N, K, device):
 
 @pytest.mark.parametrize(
     "B, H, S, D, causal",
-    [(4, 8, 128, 64, True), (4, 8, 256, 32, False), (64, 8, 256, 64, False)],
+    [
+        (4, 8, 128, 64, True),
+        pytest.param(4, 8, 256, 32, False, marks=slow),
+        pytest.param(64, 8, 256, 64, False, marks=slow),
+    ],
 )
 def test_attention(ref, B, H, S, D, causal, device):
     assert S >= 64  # never below the reference's tile size (see the module docstring)

@@ -49,6 +49,7 @@ SIGNATURES = {
     "tb200_linear_bwd_bias_workspace": (c_size, [c_i64, c_i64]),
     "tb200_linear_bwd_bias": (c_int, [c_ptr] * 3 + [c_size, c_i64, c_i64, c_int, c_ptr]),
     "tb200_geglu_fwd": (c_int, [c_ptr] * 5 + [c_i64] * 9 + [c_int, c_int, c_int, c_ptr]),
+    "tb200_geglu_fwd_row_scaled": (c_int, [c_ptr] * 6 + [c_i64] * 9 + [c_int, c_int, c_ptr]),
     "tb200_geglu_bwd_elementwise": (c_int, [c_ptr] * 3 + [c_i64, c_i64, c_int, c_int, c_ptr]),
     "tb200_geglu_bwd_elementwise_bias": (c_int, [c_ptr] * 5 + [c_size, c_i64, c_i64, c_int, c_int, c_ptr]),
     "tb200_attention_fwd": (
@@ -344,6 +345,24 @@ def geglu_fwd(out, state_gate, x, w, bias, gelu_tanh, allow_tf32):
         ),
         "tb200_geglu_fwd",
     )
+
+
+def geglu_fwd_row_scaled(out, state_gate, x, w, bias, row_scale, gelu_tanh):
+    """state_gate = row_scale[m] * (x w^T) + bias and out = state * gelu(gate). Returns False when
+    the library does not take the inputs on its tensor-core path (the caller then composes
+    rms_norm and geglu); raises on any other error."""
+    _require_cuda(out, state_gate, x, w, bias, row_scale)
+    B, M, K = x.shape
+    N = w.shape[0]
+    status = load().tb200_geglu_fwd_row_scaled(
+        _ptr(out), _ptr(state_gate), _ptr(x), _ptr(w), _ptr(bias), _ptr(row_scale), B, M, N, K,
+        x.stride(0), x.stride(1), x.stride(2), w.stride(0), w.stride(1),
+        int(bool(gelu_tanh)), dtype_code(x.dtype), _stream(x),
+    )
+    if status == -2:  # TB200_ERR_UNSUPPORTED
+        return False
+    _check(status, "tb200_geglu_fwd_row_scaled")
+    return True
 
 
 def geglu_bwd_elementwise(d_state_gate, dout, state_gate, rows, N, gelu_tanh):

@@ -228,6 +228,34 @@ extern "C" int tb200_geglu_fwd(void* out, void* state_gate, const void* x, const
   return rc;
 }
 
+// GEGLU on rows that are scaled on the fly: state_gate = row_scale[m] * (x w^T) + bias. With
+// row_scale = 1 / (rms + eps) and w = W * diag(norm weight) this is GEGLU(RMSNorm(x)) without the
+// normalised copy of x ever being written or read. Tensor-core path only (16-bit, unit inner
+// strides): other inputs are refused and the caller composes the two operations instead.
+extern "C" int tb200_geglu_fwd_row_scaled(void* out, void* state_gate, const void* x, const void* w,
+                                          const void* bias, const float* row_scale, int64_t B, int64_t M,
+                                          int64_t N, int64_t K, int64_t x_sb, int64_t x_sm, int64_t x_sk,
+                                          int64_t w_sn, int64_t w_sk, int gelu_tanh, int dtype, void* stream) {
+  if (int rc = check_dims("geglu_fwd_row_scaled", B, M, N, K)) return rc;
+  if (B * M * N == 0) return 0;
+  TB200_REQUIRE(out && state_gate && x && w && row_scale, TB200_ERR_INVALID, "geglu_fwd_row_scaled: null pointer");
+  TB200_REQUIRE(N % 2 == 0, TB200_ERR_INVALID, "geglu_fwd_row_scaled: N=%lld must be even", (long long)N);
+  TB200_REQUIRE(dtype != TB200_F32 && x_sk == 1 && w_sk == 1 && (B == 1 || x_sb == M * x_sm), TB200_ERR_UNSUPPORTED,
+                "geglu_fwd_row_scaled: needs 16-bit operands with unit inner strides and a collapsible batch");
+  TcGemmArgs g;
+  g.M = B * M; g.N = N; g.K = K;
+  g.a = x; g.a_ld = x_sm; g.a_kmajor = true;
+  g.b = w; g.b_ld = w_sn; g.b_kmajor = true;
+  g.c = state_gate; g.c_ld = N; g.bias = bias;
+  g.geglu_out = out; g.gelu_tanh = gelu_tanh;
+  g.row_scale = row_scale;
+  TB200_REQUIRE(tc_gemm_supported(g, dtype), TB200_ERR_UNSUPPORTED,
+                "geglu_fwd_row_scaled: shape or alignment not taken by the tensor-core GEMM");
+  int rc = launch_gemm_tc(g, dtype, (cudaStream_t)stream);
+  if (rc == 0) note_kernel("gemm_tcgen05", 1);
+  return rc;
+}
+
 // ------------------------------------------------------------------ Attention
 static int fill_attn(AttnArgs* a, const char* who, int64_t B, int64_t H, int64_t S, int64_t D,
                      const int64_t* qs, const int64_t* ks, const int64_t* vs, const int64_t* os,

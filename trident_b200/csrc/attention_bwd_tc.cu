@@ -25,14 +25,18 @@
 //              memory and one thread adds that to the accumulator with bulk tensor reduce-add
 //              copies. (Per-thread 16-byte reductions of this layout were bound by half-used
 //              L2 sectors; M = 64 products for a transposed dQ are not used.)
-//   A last small kernel scales and rounds the accumulator.
+//   A last small kernel scales and rounds the accumulator. (Letting the CTA that adds the last
+//   part of a dQ tile convert it, behind a fence and a counter per tile, was measured: the fence
+//   after every tile's 16 K reductions cost the drain warps more than the pass it saved, 1.95 ms
+//   against 1.65 ms for the configuration [4,32,4096,128].)
 //
 // The MMA thread issues, per query tile s:  dP^T(s) | dV(s) | S^T(s+1) | dK(s) dQ(s), so the
 // tensor pipe always has the neighbouring tile's products to run while the compute warps are
 // in stage A or B (Q_i and dO_i are double-buffered in shared memory for that). The softmax
 // scale is applied once to dK in the epilogue and to dQ in the final conversion.
 //
-// A row kernel that runs first provides -delta_q = -sum_d O dO and -lse_q*log2e. The order
+// A row kernel that runs first provides -delta_q = -sum_d O dO and -lse_q*log2e, and clears the
+// fp32 dQ accumulator (no separate memset). The order
 // in which key tiles add into dQ is not fixed, so dQ can differ in the last bits from run to
 // run; dK and dV are deterministic.
 #include <mutex>
@@ -54,7 +58,10 @@ namespace {
 // warps (a key row is shared by CG threads, each taking 128 / CG query columns) and four drain
 // warps. CG is 2, except for the masked kernel at D = 64, where the compute warps are the
 // critical path (one shared-memory load per mask element) and CG = 4 halves their work.
-__host__ __device__ constexpr int cgroups_for(int D, bool masked) { return (masked && D == 64) ? 4 : 2; }
+#ifndef TB200_BWD_CG_ALL
+#define TB200_BWD_CG_ALL 2
+#endif
+__host__ __device__ constexpr int cgroups_for(int D, bool masked) { return (masked && D == 64) ? 4 : TB200_BWD_CG_ALL; }
 __host__ __device__ constexpr int bwd_threads_for(int D, bool masked) { return (4 + 4 * cgroups_for(D, masked) + 4) * 32; }
 constexpr float LOG2E = 1.4426950408889634f;
 
@@ -62,7 +69,7 @@ struct BwdParams {
   AttnArgs a;
   void* dk;
   void* dv;
-  float* dq_acc;        // [B,H,S,D] fp32, zeroed before the launch
+  float* dq_acc;        // [B,H,S,D] fp32, zeroed by the row kernel
   const float* nlse2;   // [B,H,S]  -lse * log2(e)
   const float* ndelta;  // [B,H,S]  -sum_d out*dout
   const void* mask;
@@ -590,10 +597,12 @@ __global__ void __launch_bounds__(bwd_threads_for(D, MASKED), 1)
 // ndelta = -sum_d out*dout (out strided over b, h, s; dout contiguous) and nlse2 = -lse * log2(e).
 // D / 8 threads share a (b, h, s) row, each with one 16-byte load of out and of dout, so a warp
 // covers 256 / D rows and moves 1 KB per pair of load instructions.
+// The same threads clear the row's D floats of the fp32 dQ accumulator (32 bytes each).
 template <typename T, int D>
 __global__ void __launch_bounds__(256)
     attn_bwd_prep_kernel(float* __restrict__ ndelta, float* __restrict__ nlse2, const T* __restrict__ out,
-                         const T* __restrict__ dout, const float* __restrict__ lse, AttnArgs a) {
+                         const T* __restrict__ dout, const float* __restrict__ lse, float* __restrict__ dq_acc,
+                         AttnArgs a) {
   constexpr int TPR = D / 8;           // threads per row
   constexpr int ROWS_PER_CTA = 256 / TPR;
   const int sub = threadIdx.x % TPR;
@@ -608,6 +617,10 @@ __global__ void __launch_bounds__(256)
     float o[8], g[8];
     unpack<T>(ld_stream(orow), o);
     unpack<T>(ld_stream(drow), g);
+    float4* acc_row = reinterpret_cast<float4*>(dq_acc + r * D + sub * 8);
+    acc_row[0] = make_float4(0.f, 0.f, 0.f, 0.f);
+    acc_row[1] = make_float4(0.f, 0.f, 0.f, 0.f);
+
 #pragma unroll
     for (int i = 0; i < 8; ++i) acc = fmaf(o[i], g[i], acc);
   }
@@ -623,11 +636,12 @@ template <typename T>
 __global__ void dq_convert_kernel(T* __restrict__ dq, const float* __restrict__ acc, long long n, float scale) {
   const long long i = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 8;
   if (i >= n) return;
-  const float4 a = *reinterpret_cast<const float4*>(acc + i);
-  const float4 c = *reinterpret_cast<const float4*>(acc + i + 4);
-  const float v[8] = {a.x * scale, a.y * scale, a.z * scale, a.w * scale,
-                      c.x * scale, c.y * scale, c.z * scale, c.w * scale};
-  *reinterpret_cast<uint4*>(dq + i) = pack<T>(v);
+  // streamed once: kept out of L1
+  const uint4 ra = ld_stream(acc + i), rc = ld_stream(acc + i + 4);
+  const float v[8] = {__uint_as_float(ra.x) * scale, __uint_as_float(ra.y) * scale, __uint_as_float(ra.z) * scale,
+                      __uint_as_float(ra.w) * scale, __uint_as_float(rc.x) * scale, __uint_as_float(rc.y) * scale,
+                      __uint_as_float(rc.z) * scale, __uint_as_float(rc.w) * scale};
+  st_stream(dq + i, pack<T>(v));
 }
 
 using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -686,7 +700,8 @@ static int launch_bwd(const CUtensorMap& mq, const CUtensorMap& mk, const CUtens
 }  // namespace
 
 // scratch: [ndelta | nlse2] (2 * B*H*S floats, 256-byte aligned) followed by the fp32 dq
-// accumulator (B*H*S*D floats). Launches: prep, memset, main kernel, dq convert.
+// accumulator (B*H*S*D floats). Launches: row kernel (which also clears the accumulator), main
+// kernel, dq conversion.
 int launch_attn_bwd_tc(void* dq, void* dk, void* dv, const void* dout, const void* q, const void* k,
                        const void* v, const void* out, const float* lse, float* row_scratch, float* dq_acc,
                        const void* mask, const AttnArgs& a, int dtype, cudaStream_t st) {
@@ -702,11 +717,6 @@ int launch_attn_bwd_tc(void* dq, void* dk, void* dv, const void* dout, const voi
   const long long n = rows * a.D;
   float* ndelta = row_scratch;
   float* nlse2 = row_scratch + rows;
-  cudaError_t e = cudaMemsetAsync(dq_acc, 0, (size_t)n * sizeof(float), st);
-  if (e != cudaSuccess) {
-    set_error("attention_bwd: memset of the dq accumulator failed: %s", cudaGetErrorString(e));
-    return (int)e;
-  }
   BwdParams p;
   CUtensorMap mmask = mq;  // placeholder when no mask tile is staged
   p.mask_tma = 0;
@@ -737,7 +747,7 @@ int launch_attn_bwd_tc(void* dq, void* dk, void* dv, const void* dout, const voi
     using T = decltype(tag);
     constexpr int D = decltype(dsel)::value;
     attn_bwd_prep_kernel<T, D><<<(unsigned)ceil_div(rows, 256 / (D / 8)), 256, 0, st>>>(
-        ndelta, nlse2, (const T*)out, (const T*)dout, lse, a);
+        ndelta, nlse2, (const T*)out, (const T*)dout, lse, dq_acc, a);
     int rc = launch_status("attn_bwd_prep");
     if (rc) return rc;
     if (a.causal)

@@ -60,6 +60,7 @@ struct GemmParams {
   void* geglu_out;      // [M, N/2] or null
   int gelu_tanh;
   int* status;
+  const float* row_scale;  // nullable: per-row factor applied to the accumulator (fused RMSNorm)
 };
 
 template <typename T>
@@ -250,6 +251,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
       ptx::tc_fence_after();
       const int row = m0 + quarter * 32 + lane;
       const uint32_t t_row = tmem_base + acc * BN + (static_cast<uint32_t>(quarter * 32) << 16);
+      const float rs = (p.row_scale && row < p.M) ? __ldg(p.row_scale + row) : 1.f;
       if constexpr (!GEGLU) {
         const int n0 = n_tile * BN;
 #pragma unroll 1
@@ -261,7 +263,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
           ptx::tmem_ld_wait();
           float v[32];
 #pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * rs;
           const int valid = min(32, p.N - col);
           if (bias) {
 #pragma unroll
@@ -278,16 +280,16 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
         for (int c = 0; c < BN / 64; ++c) {
           const int col = n0 + c * 32;
           if (col >= X) break;
-          uint32_t rs[32], rg[32];
-          ptx::tmem_ld32(t_row + c * 32, rs);
+          uint32_t rs_[32], rg[32];
+          ptx::tmem_ld32(t_row + c * 32, rs_);
           ptx::tmem_ld32(t_row + BN / 2 + c * 32, rg);
           ptx::tmem_ld_wait();
           float s[32], g[32];
           const int valid = min(32, X - col);
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
-            s[i] = __uint_as_float(rs[i]);
-            g[i] = __uint_as_float(rg[i]);
+            s[i] = __uint_as_float(rs_[i]) * rs;
+            g[i] = __uint_as_float(rg[i]) * rs;
             if (bias && i < valid) {
               s[i] += Traits<T>::to_f(__ldg(bias + col + i));
               g[i] += Traits<T>::to_f(__ldg(bias + X + col + i));
@@ -448,6 +450,7 @@ int launch_gemm_tc(const TcGemmArgs& g, int dtype, cudaStream_t st) {
   p.bias = g.bias;
   p.geglu_out = g.geglu_out;
   p.gelu_tanh = g.gelu_tanh;
+  p.row_scale = g.row_scale;
   p.status = device_status_ptr();
 
   const bool bf = dtype == TB200_BF16;

@@ -26,6 +26,7 @@ struct TcGemmArgs {
   const void* bias = nullptr;
   void* geglu_out = nullptr;
   int gelu_tanh = 0;
+  const float* row_scale = nullptr;  // [M]: the accumulator row is multiplied by it before the bias
 };
 
 bool tc_gemm_supported(const TcGemmArgs& g, int dtype);

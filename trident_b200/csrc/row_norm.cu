@@ -313,7 +313,7 @@ __global__ void __launch_bounds__(CTA_ROW ? 512 : 256, CTA_ROW ? 2 : 4)
 #pragma unroll
     for (int c = 0; c < CHUNKS; ++c) {
       const int col = rt.template col<VEC>(c);
-      if (col < cols) {
+      if (y && col < cols) {  // y == null: only the row statistic is wanted
         uint64_t t[PAIRS], ws[PAIRS], bs[PAIRS];
         unpack2<T>(raw[c], t);
         unpack2<T>(EARLY ? wraw[EARLY ? c : 0] : ld_cached(w + col), ws);
@@ -344,7 +344,7 @@ __global__ void rms_fwd_generic(T* y, float* rms, const T* x, const T* w, const 
   }
   const float r = sqrtf(warp_sum(s) / (float)partial);
   const float inv = 1.f / (r + eps);
-  for (int64_t i = lane; i < cols; i += 32) {
+  for (int64_t i = lane; y && i < cols; i += 32) {  // y == null: only the row statistic is wanted
     float o = Traits<T>::to_f(xr[i * cs_]) * inv * Traits<T>::to_f(w[i]);
     if (b) o += Traits<T>::to_f(b[i]);
     y[row * cols + i] = Traits<T>::from_f(o);
@@ -562,12 +562,12 @@ extern "C" int tb200_rms_norm_fwd(void* y, float* rms, const void* x, const void
                 "rms_norm_fwd: partial_cols %lld outside (0, %lld]", (long long)partial_cols,
                 (long long)cols);
   if (rows == 0) return 0;
-  TB200_REQUIRE(y && rms && x && weight, TB200_ERR_INVALID, "rms_norm_fwd: null pointer");
+  TB200_REQUIRE(rms && x && weight, TB200_ERR_INVALID, "rms_norm_fwd: null pointer");
   cudaStream_t st = (cudaStream_t)stream;
   return dispatch_dtype(dtype, [&](auto tag) -> int {
     using T = decltype(tag);
     constexpr int VEC = Traits<T>::VEC;
-    const bool ok = aligned16(y) && aligned16(x) && aligned16(weight) &&
+    const bool ok = (!y || aligned16(y)) && aligned16(x) && aligned16(weight) &&
                     (!bias || aligned16(bias)) && col_stride == 1 && row_stride % VEC == 0 &&
                     row_stride >= cols && cols < (1 << 30);
     RowPlan p = plan_rows<T>(cols, ok);
