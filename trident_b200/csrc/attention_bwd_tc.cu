@@ -64,6 +64,20 @@ namespace {
 __host__ __device__ constexpr int cgroups_for(int D, bool masked) { return (masked && D == 64) ? 4 : TB200_BWD_CG_ALL; }
 __host__ __device__ constexpr int bwd_threads_for(int D, bool masked) { return (4 + 4 * cgroups_for(D, masked) + 4) * 32; }
 constexpr float LOG2E = 1.4426950408889634f;
+// Register allowances at D = 128 (512 threads, launched with 128 registers each): the drain warps
+// take the whole dQ tile into registers (128 values a thread) so that tensor memory is released
+// before the first reduction is issued; the service and compute warps give registers back.
+constexpr int BWD_REGS_LAUNCH = 128, BWD_REGS_SERVICE = 96, BWD_REGS_COMPUTE = 120, BWD_REGS_DRAIN = 168;
+static_assert(4 * 32 * BWD_REGS_SERVICE + 8 * 32 * BWD_REGS_COMPUTE + 4 * 32 * BWD_REGS_DRAIN <= BWD_REGS_LAUNCH * 512,
+              "register pool of the CTA exceeded: setmaxnreg.inc would never return");
+
+// Tensor-memory column (relative to the tile's first column) of the packed 16-bit copy of 32-bit
+// chunk c (32 query columns) of a P^T or dS^T row: each compute thread packs into the columns it
+// has just read itself (its NCH chunks), so no thread overwrites columns another thread still
+// has to read and no barrier between the owners of a row is needed.
+__host__ __device__ constexpr uint32_t packed_col(int c, int nch) {
+  return static_cast<uint32_t>((c / nch) * (32 * nch) + (c % nch) * 16);
+}
 
 struct BwdParams {
   AttnArgs a;
@@ -234,6 +248,17 @@ __global__ void __launch_bounds__(bwd_threads_for(D, MASKED), 1)
   ptx::tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
+  // (warpgroups: warps 0-3 service, 4-11 compute, 12-15 drain; an increase waits until the
+  // CTA's own pool holds the request, which the static_assert above and the host's check of the
+  // compiled register count guarantee)
+#ifndef TB200_BWD_REBALANCE
+#define TB200_BWD_REBALANCE 1
+#endif
+  constexpr bool REBALANCE = DQ_T && !MASKED && TB200_BWD_REBALANCE;
+  static_assert(!REBALANCE || bwd_threads_for(D, MASKED) == 512, "allowances are written for 16 warps");
+
+  if (warp < 4) {
+  if constexpr (REBALANCE) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(BWD_REGS_SERVICE));
   if (warp == 0 && lane == 0) {
     // ---------------------------------------------------------------- producer
     ptx::mbar_expect_tx(kv_full, 2 * TILE_BYTES);
@@ -305,8 +330,8 @@ __global__ void __launch_bounds__(bwd_threads_for(D, MASKED), 1)
       ptx::mbar_wait(p1_ready, ph, abort_flag, p.status, 45);
       ptx::tc_fence_after();
 #pragma unroll
-      for (int ks = 0; ks < 8; ++ks)
-        ptx::umma_ts(tmem_base + COL_DV, tmem_base + COL_ST + ks * 8,
+      for (int ks = 0; ks < 8; ++ks)  // (16 query columns per step: half of a packed chunk)
+        ptx::umma_ts(tmem_base + COL_DV, tmem_base + COL_ST + packed_col(ks >> 1, NCH) + (ks & 1) * 8,
                      ptx::make_smem_desc(da + ks * 2048, BOX_BYTES, 1024), IDESC_DKV, (s | ks) != 0);
       // S^T(s+1): overwrites P^T(s), which the dV products above read first (in-order pipe)
       if (s + 1 < steps) {
@@ -315,12 +340,15 @@ __global__ void __launch_bounds__(bwd_threads_for(D, MASKED), 1)
         issue_st(st ^ 1);
         ptx::umma_commit(st_ready);
       }
-      // dK += dS^T Q, then dQ = dS K into the dP^T columns
+      // dK += dS^T Q (dS^T from tensor memory), then dQ = dS K into the dP^T columns. (dK with dS^T
+      // taken from shared memory, which would let dQ go first, was measured: with both operands
+      // of four of the five products coming from shared memory the tensor pipe waits for
+      // operands, 133 cycles per instruction on average instead of 75.)
       ptx::mbar_wait(p2_ready, ph, abort_flag, p.status, 47);
       ptx::tc_fence_after();
 #pragma unroll
       for (int ks = 0; ks < 8; ++ks)
-        ptx::umma_ts(tmem_base + COL_DK, tmem_base + COL_DPT + ks * 8,
+        ptx::umma_ts(tmem_base + COL_DK, tmem_base + COL_DPT + packed_col(ks >> 1, NCH) + (ks & 1) * 8,
                      ptx::make_smem_desc(qa + ks * 2048, BOX_BYTES, 1024), IDESC_DKV, (s | ks) != 0);
       ptx::umma_commit(&qdo_empty[st]);  // Q_s and dO_s are dead once dK(s) has run
       if constexpr (DQ_T) {
@@ -341,8 +369,10 @@ __global__ void __launch_bounds__(bwd_threads_for(D, MASKED), 1)
     // everything it issued has completed (the compute warps wait for the same barrier, but after
     // an aborted wait they may pass it early).
     ptx::mbar_wait_drain(all_done, 0, abort_flag, p.status, 53);
-  } else if (warp >= 4 && warp < DRAIN_WARP0) {
+  }
+  } else if (warp < DRAIN_WARP0) {
     // ---------------------------------------------------------------- P^T / dS^T (lane = key row)
+    if constexpr (REBALANCE) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(BWD_REGS_COMPUTE));
     // warps 4-7 take the first 128 / CGROUPS query columns of their rows, warps 8-11 the next, ...
     const int quarter = warp & 3;
     const int cgrp = (warp - 4) >> 2;
@@ -371,7 +401,10 @@ __global__ void __launch_bounds__(bwd_threads_for(D, MASKED), 1)
       {
         uint32_t ra[32];
         [[maybe_unused]] uint32_t rb[32];
-        auto stage_a = [&](const uint32_t (&sv)[32], int c, int lc) {
+        // `diag_tag` is a compile-time flag: only the tile on the diagonal pays for the per-element
+        // comparison (with a run-time flag every tile of the causal kernel carried it)
+        auto stage_a = [&](const uint32_t (&sv)[32], int c, int lc, auto diag_tag) {
+          constexpr bool DIAG = decltype(diag_tag)::value;
 #pragma unroll
           for (int g = 0; g < 8; ++g) {
             const float4 nl = nlse4[c * 8 + g];
@@ -397,7 +430,7 @@ __global__ void __launch_bounds__(bwd_threads_for(D, MASKED), 1)
               }
             }
             float p0 = am::ex2(x0), p1 = am::ex2(x1), p2 = am::ex2(x2), p3 = am::ex2(x3);
-            if (diag) {  // query index below the key index contributes nothing
+            if constexpr (DIAG) {  // query index below the key index contributes nothing
               const int col = c * 32 + g * 4;
               if (col + 0 < r) p0 = 0.f;
               if (col + 1 < r) p1 = 0.f;
@@ -411,20 +444,20 @@ __global__ void __launch_bounds__(bwd_threads_for(D, MASKED), 1)
         ptx::tmem_ld32(st_addr + c0 * 32, ra);
         am::tmem_ld_wait_dep(ra);
         if constexpr (NCH == 2) ptx::tmem_ld32(st_addr + c0 * 32 + 32, rb);
-        stage_a(ra, c0, 0);
+        if (diag) stage_a(ra, c0, 0, std::true_type{});
+        else stage_a(ra, c0, 0, std::false_type{});
         if constexpr (NCH == 2) {
           am::tmem_ld_wait_dep(rb);
-          stage_a(rb, c0 + 1, 1);
+          if (diag) stage_a(rb, c0 + 1, 1, std::true_type{});
+          else stage_a(rb, c0 + 1, 1, std::false_type{});
         }
-        // all owners of a key row (this warp and its partners four warps apart) must have read
-        // their S^T columns before any of them overwrites them with packed P^T
-        asm volatile("bar.sync 1, %0;" ::"n"(COMPUTE_WARPS * 32) : "memory");
+        // packed P^T goes over this thread's own S^T columns (see packed_col)
 #pragma unroll
         for (int lc = 0; lc < NCH; ++lc) {
           uint32_t chunk[16];
 #pragma unroll
           for (int i = 0; i < 16; ++i) chunk[i] = pp[lc * 16 + i];
-          ptx::tmem_st16(st_addr + (c0 + lc) * 16, chunk);
+          ptx::tmem_st16(st_addr + packed_col(c0 + lc, NCH), chunk);
         }
         ptx::tmem_st_wait();
         ptx::tc_fence_before();
@@ -475,13 +508,13 @@ __global__ void __launch_bounds__(bwd_threads_for(D, MASKED), 1)
           am::tmem_ld_wait_dep(rb);
           stage_b(rb, c0 + 1, 1);
         }
-        asm volatile("bar.sync 1, %0;" ::"n"(COMPUTE_WARPS * 32) : "memory");  // dP^T fully read before dS^T overwrites it
+        // packed dS^T over this thread's own dP^T columns (for dK) besides the shared-memory copy (for dQ)
 #pragma unroll
         for (int lc = 0; lc < NCH; ++lc) {
           uint32_t chunk[16];
 #pragma unroll
           for (int i = 0; i < 16; ++i) chunk[i] = pp[lc * 16 + i];
-          ptx::tmem_st16(dp_addr + (c0 + lc) * 16, chunk);
+          ptx::tmem_st16(dp_addr + packed_col(c0 + lc, NCH), chunk);
         }
         ptx::tmem_st_wait();
         ptx::fence_proxy_async_smem();
@@ -517,8 +550,9 @@ __global__ void __launch_bounds__(bwd_threads_for(D, MASKED), 1)
         *reinterpret_cast<uint4*>(dst + g * 8) = o;
       }
     }
-  } else if (warp >= DRAIN_WARP0) {
+  } else {
     // ---------------------------------------------------------------- dQ drain
+    if constexpr (REBALANCE) asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(BWD_REGS_DRAIN));
     const int quarter = warp & 3;
     const int r = quarter * 32 + lane;
     const uint32_t dq_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + COL_DQ;
@@ -530,28 +564,51 @@ __global__ void __launch_bounds__(bwd_threads_for(D, MASKED), 1)
       if constexpr (DQ_T) {
         // lane = feature d: this thread owns feature d = r of the tile's 128 query rows
         float* dst = p.dq_acc + (row_base + (long long)it * 128) * D + r;
-        // Three of the four 32-column blocks are loaded at once; the fourth reuses the
-        // registers of the first after its reductions are issued, so that only 32 of the
-        // 128 reductions stand between the product and the release of the tensor memory.
-        uint32_t r0[32], r1[32], r2[32];
-        ptx::tmem_ld32(dq_addr, r0);
-        ptx::tmem_ld32(dq_addr + 32, r1);
-        ptx::tmem_ld32(dq_addr + 64, r2);
-        am::tmem_ld_wait_dep(r0);
-        am::tmem_ld_wait_dep(r1);
-        am::tmem_ld_wait_dep(r2);
+        if constexpr (REBALANCE) {
+          // the whole tile goes to registers, tensor memory is released, then the 128 reductions
+          uint32_t r0[32], r1[32], r2[32], r3[32];
+          ptx::tmem_ld32(dq_addr, r0);
+          ptx::tmem_ld32(dq_addr + 32, r1);
+          ptx::tmem_ld32(dq_addr + 64, r2);
+          ptx::tmem_ld32(dq_addr + 96, r3);
+          am::tmem_ld_wait_dep(r0);
+          am::tmem_ld_wait_dep(r1);
+          am::tmem_ld_wait_dep(r2);
+          am::tmem_ld_wait_dep(r3);
+          ptx::tc_fence_before();
+          ptx::mbar_arrive(dq_drained);
 #pragma unroll
-        for (int i = 0; i < 32; ++i) red_add_f32(dst + (long long)i * D, __uint_as_float(r0[i]));
-        ptx::tmem_ld32(dq_addr + 96, r0);
-        am::tmem_ld_wait_dep(r0);
-        ptx::tc_fence_before();
-        ptx::mbar_arrive(dq_drained);  // tensor memory released as soon as its values sit in registers
+          for (int i = 0; i < 32; ++i) red_add_f32(dst + (long long)i * D, __uint_as_float(r0[i]));
 #pragma unroll
-        for (int i = 0; i < 32; ++i) red_add_f32(dst + (long long)(32 + i) * D, __uint_as_float(r1[i]));
+          for (int i = 0; i < 32; ++i) red_add_f32(dst + (long long)(32 + i) * D, __uint_as_float(r1[i]));
 #pragma unroll
-        for (int i = 0; i < 32; ++i) red_add_f32(dst + (long long)(64 + i) * D, __uint_as_float(r2[i]));
+          for (int i = 0; i < 32; ++i) red_add_f32(dst + (long long)(64 + i) * D, __uint_as_float(r2[i]));
 #pragma unroll
-        for (int i = 0; i < 32; ++i) red_add_f32(dst + (long long)(96 + i) * D, __uint_as_float(r0[i]));
+          for (int i = 0; i < 32; ++i) red_add_f32(dst + (long long)(96 + i) * D, __uint_as_float(r3[i]));
+        } else {
+          // Three of the four 32-column blocks are loaded at once; the fourth reuses the
+          // registers of the first after its reductions are issued, so that only 32 of the
+          // 128 reductions stand between the product and the release of the tensor memory.
+          uint32_t r0[32], r1[32], r2[32];
+          ptx::tmem_ld32(dq_addr, r0);
+          ptx::tmem_ld32(dq_addr + 32, r1);
+          ptx::tmem_ld32(dq_addr + 64, r2);
+          am::tmem_ld_wait_dep(r0);
+          am::tmem_ld_wait_dep(r1);
+          am::tmem_ld_wait_dep(r2);
+#pragma unroll
+          for (int i = 0; i < 32; ++i) red_add_f32(dst + (long long)i * D, __uint_as_float(r0[i]));
+          ptx::tmem_ld32(dq_addr + 96, r0);
+          am::tmem_ld_wait_dep(r0);
+          ptx::tc_fence_before();
+          ptx::mbar_arrive(dq_drained);  // tensor memory released as soon as its values sit in registers
+#pragma unroll
+          for (int i = 0; i < 32; ++i) red_add_f32(dst + (long long)(32 + i) * D, __uint_as_float(r1[i]));
+#pragma unroll
+          for (int i = 0; i < 32; ++i) red_add_f32(dst + (long long)(64 + i) * D, __uint_as_float(r2[i]));
+#pragma unroll
+          for (int i = 0; i < 32; ++i) red_add_f32(dst + (long long)(96 + i) * D, __uint_as_float(r0[i]));
+        }
       } else {
         // lane = query row; dQ_i leaves through a staging tile of D/32 boxes of [128 rows][32
         // floats] (16 KB each) and bulk tensor reduce-add copies
@@ -691,6 +748,28 @@ static int launch_bwd(const CUtensorMap& mq, const CUtensorMap& mk, const CUtens
   if (attr_err != cudaSuccess) {
     set_error("attention_bwd: cudaFuncSetAttribute failed: %s", cudaGetErrorString(attr_err));
     return (int)attr_err;
+  }
+  if constexpr (D == 128 && !MASKED && TB200_BWD_REBALANCE) {
+    // the kernel's setmaxnreg.inc has no bound on its wait: refuse to launch a build whose register
+    // pool (registers per thread at launch x threads) cannot hold the allowances it will ask for
+    static std::atomic<int> regs_cached{0};
+    int regs = regs_cached.load(std::memory_order_relaxed);
+    if (regs == 0) {
+      cudaFuncAttributes fa;
+      const cudaError_t e = cudaFuncGetAttributes(&fa, kern);
+      if (e != cudaSuccess) {
+        set_error("attention_bwd: cudaFuncGetAttributes failed: %s", cudaGetErrorString(e));
+        return (int)e;
+      }
+      regs = fa.numRegs;
+      regs_cached.store(regs, std::memory_order_relaxed);
+    }
+    if (regs * 512 < 4 * 32 * BWD_REGS_SERVICE + 8 * 32 * BWD_REGS_COMPUTE + 4 * 32 * BWD_REGS_DRAIN ||
+        regs < BWD_REGS_COMPUTE) {
+      set_error("attention_bwd: kernel compiled with %d registers per thread, the register rebalancing needs %d",
+                regs, BWD_REGS_LAUNCH);
+      return TB200_ERR_UNSUPPORTED;
+    }
   }
   dim3 grid((unsigned)p.nq, (unsigned)(p.a.B * p.a.H));
   kern<<<grid, bwd_threads_for(D, MASKED), SMEM, st>>>(mq, mk, mv, md, mdq, mmask, p);

@@ -52,7 +52,10 @@ constexpr int FWD_THREADS = 384;
 constexpr int REGS_LAUNCH = 168, REGS_SERVICE = 56, REGS_SOFTMAX = 224;
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr float LN2 = 0.6931471805599453f;
-constexpr float RESCALE_THRESHOLD = 8.f;
+#ifndef TB200_RESCALE_THRESHOLD
+#define TB200_RESCALE_THRESHOLD 8.f
+#endif
+constexpr float RESCALE_THRESHOLD = TB200_RESCALE_THRESHOLD;
 // The exponential passes of the two query tiles take turns (named barriers 1 and 2, see the
 // softmax loop): 1 = on.
 #ifndef TB200_FWD_ALTERNATE
@@ -336,24 +339,37 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
     auto commit_ = [&](uint64_t* bar) {
       if (elected) ptx::umma_commit(bar);
     };
+    // Shared-memory descriptors are built once: per product only the 14-bit address field moves,
+    // by a compile-time constant per K step. (The issuing warp shares its scheduler with two
+    // softmax warps that issue almost every cycle; with the descriptors rebuilt per instruction the
+    // issue of one tcgen05.mma took about 80 cycles, more than the 64 the instruction needs on the
+    // tensor pipe.)
+    const uint64_t dq0 = ptx::make_smem_desc(ptx::smem_u32(q_smem), 16, 1024);
+    const uint64_t dk0 = ptx::make_smem_desc(ptx::smem_u32(k_smem), 16, 1024);
+    const uint64_t dv0 = ptx::make_smem_desc(ptx::smem_u32(v_smem), BOX_BYTES, 1024);
+    constexpr uint64_t NEXT_TILE = static_cast<uint64_t>(TILE_BYTES >> 4);  // second query tile / second stage
     auto issue_qk = [&](int t, int st) {
-      const uint32_t qa = ptx::smem_u32(q_smem + t * TILE_BYTES);
-      const uint32_t ka = ptx::smem_u32(k_smem + st * TILE_BYTES);
+      const uint64_t qd = dq0 + (t ? NEXT_TILE : 0), kd = dk0 + (st ? NEXT_TILE : 0);
+      const uint32_t d_tmem = tmem_base + COL_S + t * 128;
+      // (every lane walks the unrolled loop and the elected one issues: with the eight
+      // instructions inside one `if (elected)` block the unpaired last query tile of an odd
+      // tile count came out wrong in some runs; the cause was not found, this form is the one
+      // that has always been correct)
 #pragma unroll
       for (int ks = 0; ks < D / 16; ++ks) {
-        const uint32_t off = (ks >> 2) * BOX_BYTES + (ks & 3) * 32;
-        if (elected)
-          ptx::umma_ss(tmem_base + COL_S + t * 128, ptx::make_smem_desc(qa + off, 16, 1024),
-                       ptx::make_smem_desc(ka + off, 16, 1024), IDESC_QK, ks != 0);
+        const uint64_t off = static_cast<uint64_t>(((ks >> 2) * BOX_BYTES + (ks & 3) * 32) >> 4);
+        if (elected) ptx::umma_ss(d_tmem, qd + off, kd + off, IDESC_QK, ks != 0);
       }
     };
     auto issue_pv = [&](int t, int st, bool accumulate) {
-      const uint32_t va = ptx::smem_u32(v_smem + st * TILE_BYTES);
+      const uint64_t vd = dv0 + (st ? NEXT_TILE : 0);
+      const uint32_t d_tmem = tmem_base + COL_O + t * D;
+      const uint32_t p_tmem = tmem_base + (P_SPLIT ? COL_P + t * 64 : COL_S + t * 128);
 #pragma unroll
       for (int ks = 0; ks < TK / 16; ++ks) {
         if (elected)
-          ptx::umma_ts(tmem_base + COL_O + t * D, tmem_base + (P_SPLIT ? COL_P + t * 64 : COL_S + t * 128) + ks * 8,
-                       ptx::make_smem_desc(va + ks * 2048, BOX_BYTES, 1024), IDESC_PV, accumulate || ks != 0);
+          ptx::umma_ts(d_tmem, p_tmem + ks * 8, vd + static_cast<uint64_t>((ks * 2048) >> 4), IDESC_PV,
+                       accumulate || ks != 0);
       }
     };
     wait_(&q_full[0], 0, 21);
