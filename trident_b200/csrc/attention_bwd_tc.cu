@@ -95,11 +95,11 @@ struct BwdParams {
 };
 
 __device__ inline void tma_load_4d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int x, int y, int z,
-                                   int w) {
+                                   int w, uint64_t l2_policy) {
   asm volatile(
-      "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], "
-      "[%2];" ::"r"(ptx::smem_u32(smem_dst)),
-      "l"(map), "r"(ptx::smem_u32(bar)), "r"(x), "r"(y), "r"(z), "r"(w)
+      "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes.L2::cache_hint "
+      "[%0], [%1, {%3, %4, %5, %6}], [%2], %7;" ::"r"(ptx::smem_u32(smem_dst)),
+      "l"(map), "r"(ptx::smem_u32(bar)), "r"(x), "r"(y), "r"(z), "r"(w), "l"(l2_policy)
       : "memory");
 }
 // 1-D bulk copy global -> shared (16-byte aligned, size a multiple of 16).
@@ -261,11 +261,12 @@ __global__ void __launch_bounds__(bwd_threads_for(D, MASKED), 1)
   if constexpr (REBALANCE) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(BWD_REGS_SERVICE));
   if (warp == 0 && lane == 0) {
     // ---------------------------------------------------------------- producer
+    const uint64_t keep = ptx::l2_policy_evict_last(), once = ptx::l2_policy_evict_first();
     ptx::mbar_expect_tx(kv_full, 2 * TILE_BYTES);
 #pragma unroll
     for (int c = 0; c < NBOX; ++c) {
-      tma_load_4d(k_smem + c * BOX_BYTES, &map_k, kv_full, c * 64, jt * 128, h, b);
-      tma_load_4d(v_smem + c * BOX_BYTES, &map_v, kv_full, c * 64, jt * 128, h, b);
+      tma_load_4d(k_smem + c * BOX_BYTES, &map_k, kv_full, c * 64, jt * 128, h, b, once);
+      tma_load_4d(v_smem + c * BOX_BYTES, &map_v, kv_full, c * 64, jt * 128, h, b, once);
     }
     for (int s = 0; s < steps; ++s) {
       const int it = i_begin + (s + jt) % steps;  // staggered start: CTAs of one head add into different dQ tiles
@@ -277,12 +278,12 @@ __global__ void __launch_bounds__(bwd_threads_for(D, MASKED), 1)
 #pragma unroll
         for (int bx = 0; bx < 2; ++bx)
           tma_load_4d(mask_smem + st * MASK_TILE_BYTES + bx * BOX_BYTES, &map_mask, &qdo_full[st],
-                      jt * 128 + 64 * bx, it * 128, p.mask_has_h ? h : 0, p.mask_has_b ? b : 0);
+                      jt * 128 + 64 * bx, it * 128, p.mask_has_h ? h : 0, p.mask_has_b ? b : 0, once);
       }
 #pragma unroll
       for (int c = 0; c < NBOX; ++c) {
-        tma_load_4d(q_smem + st * TILE_BYTES + c * BOX_BYTES, &map_q, &qdo_full[st], c * 64, it * 128, h, b);
-        tma_load_4d(do_smem + st * TILE_BYTES + c * BOX_BYTES, &map_do, &qdo_full[st], c * 64, it * 128, h, b);
+        tma_load_4d(q_smem + st * TILE_BYTES + c * BOX_BYTES, &map_q, &qdo_full[st], c * 64, it * 128, h, b, keep);
+        tma_load_4d(do_smem + st * TILE_BYTES + c * BOX_BYTES, &map_do, &qdo_full[st], c * 64, it * 128, h, b, keep);
       }
       const long long row0 = ((long long)b * p.a.H + h) * p.a.S + (long long)it * 128;
       bulk_load(nlse_smem + st * 128, p.nlse2 + row0, 512, &qdo_full[st]);

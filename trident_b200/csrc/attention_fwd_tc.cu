@@ -95,11 +95,11 @@ __device__ inline uint32_t pack_pair<__half>(float a, float b) {
 }
 
 __device__ inline void tma_load_4d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int x, int y, int z,
-                                   int w) {
+                                   int w, uint64_t l2_policy) {
   asm volatile(
-      "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], "
-      "[%2];" ::"r"(ptx::smem_u32(smem_dst)),
-      "l"(map), "r"(ptx::smem_u32(bar)), "r"(x), "r"(y), "r"(z), "r"(w)
+      "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes.L2::cache_hint "
+      "[%0], [%1, {%3, %4, %5, %6}], [%2], %7;" ::"r"(ptx::smem_u32(smem_dst)),
+      "l"(map), "r"(ptx::smem_u32(bar)), "r"(x), "r"(y), "r"(z), "r"(w), "l"(l2_policy)
       : "memory");
 }
 
@@ -258,15 +258,16 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
     asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(REGS_SERVICE));
   if (warp == 0 && lane == 0) {
     // ---------------------------------------------------------------- producer
+    const uint64_t keep = ptx::l2_policy_evict_last(), once = ptx::l2_policy_evict_first();
     ptx::mbar_expect_tx(&q_full[0], TILE_BYTES);
 #pragma unroll
     for (int c = 0; c < NBOX; ++c)
-      tma_load_4d(q_smem + c * BOX_BYTES, &map_q, &q_full[0], c * 64, qt0 * TQ, h, b);
+      tma_load_4d(q_smem + c * BOX_BYTES, &map_q, &q_full[0], c * 64, qt0 * TQ, h, b, once);
     if (active1) {
       ptx::mbar_expect_tx(&q_full[1], TILE_BYTES);
 #pragma unroll
       for (int c = 0; c < NBOX; ++c)
-        tma_load_4d(q_smem + TILE_BYTES + c * BOX_BYTES, &map_q, &q_full[1], c * 64, qt1 * TQ, h, b);
+        tma_load_4d(q_smem + TILE_BYTES + c * BOX_BYTES, &map_q, &q_full[1], c * 64, qt1 * TQ, h, b, once);
     }
     for (int j = 0; j < nmax; ++j) {
       const int st = j & 1;
@@ -276,13 +277,13 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
         ptx::mbar_expect_tx(&k_full[st], TILE_BYTES);
 #pragma unroll
         for (int c = 0; c < NBOX; ++c)
-          tma_load_4d(k_smem + st * TILE_BYTES + c * BOX_BYTES, &map_k, &k_full[st], c * 64, j * TK, h, b);
+          tma_load_4d(k_smem + st * TILE_BYTES + c * BOX_BYTES, &map_k, &k_full[st], c * 64, j * TK, h, b, keep);
       }
       ptx::mbar_wait(&v_empty[st], ph ^ 1, abort_flag, p.status, 12);
       ptx::mbar_expect_tx(&v_full[st], TILE_BYTES);
 #pragma unroll
       for (int c = 0; c < NBOX; ++c)
-        tma_load_4d(v_smem + st * TILE_BYTES + c * BOX_BYTES, &map_v, &v_full[st], c * 64, j * TK, h, b);
+        tma_load_4d(v_smem + st * TILE_BYTES + c * BOX_BYTES, &map_v, &v_full[st], c * 64, j * TK, h, b, keep);
     }
     // Drain: the CTA's shared memory is given up when the CTA ends, so every copy issued above
     // must have landed by then. On the normal path the MMA issuer has consumed them all; after an
@@ -303,6 +304,7 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
     //     fence.proxy.async, since the next access to the stage is this bulk copy (async proxy).
     //   mask_full -> softmax threads: completes when the copy's bytes have landed (complete_tx).
     if (p.mask_tma) {
+      const uint64_t once = ptx::l2_policy_evict_first();
       for (int j = 0; j < nmax; ++j) {
         const int stg = j & 1;
         const uint32_t ph = (j >> 1) & 1;
@@ -316,7 +318,7 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
 #pragma unroll
             for (int c = 0; c < 2; ++c)
               tma_load_4d(dst + c * BOX_BYTES, &map_mask, full, j * TK + c * 64, (t == 0 ? qt0 : qt1) * TQ,
-                          p.mask_has_h ? h : 0, p.mask_has_b ? b : 0);
+                          p.mask_has_h ? h : 0, p.mask_has_b ? b : 0, once);
           }
         }
       }
