@@ -261,7 +261,13 @@ __global__ void __launch_bounds__(bwd_threads_for(D, MASKED), 1)
   if constexpr (REBALANCE) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(BWD_REGS_SERVICE));
   if (warp == 0 && lane == 0) {
     // ---------------------------------------------------------------- producer
-    const uint64_t keep = ptx::l2_policy_evict_last(), once = ptx::l2_policy_evict_first();
+#ifndef TB200_BWD_L2_KV
+#define TB200_BWD_L2_KV 1
+#define TB200_BWD_L2_QDO 0
+#define TB200_BWD_L2_MASK 0
+#endif
+    const uint64_t keep = ptx::l2_policy(TB200_BWD_L2_QDO), once = ptx::l2_policy(TB200_BWD_L2_KV);
+    const uint64_t mask_policy = ptx::l2_policy(TB200_BWD_L2_MASK);
     ptx::mbar_expect_tx(kv_full, 2 * TILE_BYTES);
 #pragma unroll
     for (int c = 0; c < NBOX; ++c) {
@@ -278,7 +284,7 @@ __global__ void __launch_bounds__(bwd_threads_for(D, MASKED), 1)
 #pragma unroll
         for (int bx = 0; bx < 2; ++bx)
           tma_load_4d(mask_smem + st * MASK_TILE_BYTES + bx * BOX_BYTES, &map_mask, &qdo_full[st],
-                      jt * 128 + 64 * bx, it * 128, p.mask_has_h ? h : 0, p.mask_has_b ? b : 0, once);
+                      jt * 128 + 64 * bx, it * 128, p.mask_has_h ? h : 0, p.mask_has_b ? b : 0, mask_policy);
       }
 #pragma unroll
       for (int c = 0; c < NBOX; ++c) {

@@ -258,7 +258,12 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
     asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(REGS_SERVICE));
   if (warp == 0 && lane == 0) {
     // ---------------------------------------------------------------- producer
-    const uint64_t keep = ptx::l2_policy_evict_last(), once = ptx::l2_policy_evict_first();
+#ifndef TB200_FWD_L2_KV
+#define TB200_FWD_L2_KV 2
+#define TB200_FWD_L2_Q 1
+#define TB200_FWD_L2_MASK 0
+#endif
+    const uint64_t keep = ptx::l2_policy(TB200_FWD_L2_KV), once = ptx::l2_policy(TB200_FWD_L2_Q);
     ptx::mbar_expect_tx(&q_full[0], TILE_BYTES);
 #pragma unroll
     for (int c = 0; c < NBOX; ++c)
@@ -304,7 +309,7 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
     //     fence.proxy.async, since the next access to the stage is this bulk copy (async proxy).
     //   mask_full -> softmax threads: completes when the copy's bytes have landed (complete_tx).
     if (p.mask_tma) {
-      const uint64_t once = ptx::l2_policy_evict_first();
+      const uint64_t once = ptx::l2_policy(TB200_FWD_L2_MASK);
       for (int j = 0; j < nmax; ++j) {
         const int stg = j & 1;
         const uint32_t ph = (j >> 1) & 1;
