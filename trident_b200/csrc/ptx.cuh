@@ -105,10 +105,8 @@ __device__ inline void tma_load_3d(void* smem_dst, const CUtensorMap* map, uint6
       ::"r"(smem_u32(smem_dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z)
       : "memory");
 }
-// L2 eviction priorities for bulk tensor loads: tiles that many CTAs read again (K and V of a head
-// in the attention forward, Q and dO in the backward) are kept, tiles that are read once (mask
-// tiles, a CTA's own Q or K/V tile) are marked as the first to go, so that a streamed operand
-// larger than L2 does not push the re-used one out.
+// L2 eviction priorities for bulk tensor loads: a tile that only one CTA ever reads (its own Q
+// tiles in the attention forward, its K/V tile in the backward) is marked as the first to go.
 __device__ inline uint64_t l2_policy_evict_first() {
   uint64_t p;
   asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
