@@ -58,10 +58,7 @@ namespace {
 // warps (a key row is shared by CG threads, each taking 128 / CG query columns) and four drain
 // warps. CG is 2, except for the masked kernel at D = 64, where the compute warps are the
 // critical path (one shared-memory load per mask element) and CG = 4 halves their work.
-#ifndef TB200_BWD_CG_ALL
-#define TB200_BWD_CG_ALL 2
-#endif
-__host__ __device__ constexpr int cgroups_for(int D, bool masked) { return (masked && D == 64) ? 4 : TB200_BWD_CG_ALL; }
+__host__ __device__ constexpr int cgroups_for(int D, bool masked) { return (masked && D == 64) ? 4 : 2; }
 __host__ __device__ constexpr int bwd_threads_for(int D, bool masked) { return (4 + 4 * cgroups_for(D, masked) + 4) * 32; }
 constexpr float LOG2E = 1.4426950408889634f;
 // Register allowances at D = 128 (512 threads, launched with 128 registers each): the drain warps
@@ -251,23 +248,16 @@ __global__ void __launch_bounds__(bwd_threads_for(D, MASKED), 1)
   // (warpgroups: warps 0-3 service, 4-11 compute, 12-15 drain; an increase waits until the
   // CTA's own pool holds the request, which the static_assert above and the host's check of the
   // compiled register count guarantee)
-#ifndef TB200_BWD_REBALANCE
-#define TB200_BWD_REBALANCE 1
-#endif
-  constexpr bool REBALANCE = DQ_T && !MASKED && TB200_BWD_REBALANCE;
+  constexpr bool REBALANCE = DQ_T && !MASKED;
   static_assert(!REBALANCE || bwd_threads_for(D, MASKED) == 512, "allowances are written for 16 warps");
 
   if (warp < 4) {
   if constexpr (REBALANCE) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(BWD_REGS_SERVICE));
   if (warp == 0 && lane == 0) {
     // ---------------------------------------------------------------- producer
-#ifndef TB200_BWD_L2_KV
-#define TB200_BWD_L2_KV 1
-#define TB200_BWD_L2_QDO 0
-#define TB200_BWD_L2_MASK 0
-#endif
-    const uint64_t keep = ptx::l2_policy(TB200_BWD_L2_QDO), once = ptx::l2_policy(TB200_BWD_L2_KV);
-    const uint64_t mask_policy = ptx::l2_policy(TB200_BWD_L2_MASK);
+    // L2 priorities (0 normal, 1 first to go): this CTA's K/V tile is read by no one else
+    const uint64_t keep = ptx::l2_policy(0), once = ptx::l2_policy(1);
+    const uint64_t mask_policy = ptx::l2_policy(0);
     ptx::mbar_expect_tx(kv_full, 2 * TILE_BYTES);
 #pragma unroll
     for (int c = 0; c < NBOX; ++c) {
@@ -756,7 +746,7 @@ static int launch_bwd(const CUtensorMap& mq, const CUtensorMap& mk, const CUtens
     set_error("attention_bwd: cudaFuncSetAttribute failed: %s", cudaGetErrorString(attr_err));
     return (int)attr_err;
   }
-  if constexpr (D == 128 && !MASKED && TB200_BWD_REBALANCE) {
+  if constexpr (D == 128 && !MASKED) {
     // the kernel's setmaxnreg.inc has no bound on its wait: refuse to launch a build whose register
     // pool (registers per thread at launch x threads) cannot hold the allowances it will ask for
     static std::atomic<int> regs_cached{0};

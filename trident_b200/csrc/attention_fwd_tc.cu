@@ -52,19 +52,7 @@ constexpr int FWD_THREADS = 384;
 constexpr int REGS_LAUNCH = 168, REGS_SERVICE = 56, REGS_SOFTMAX = 224;
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr float LN2 = 0.6931471805599453f;
-#ifndef TB200_RESCALE_THRESHOLD
-#define TB200_RESCALE_THRESHOLD 8.f
-#endif
-constexpr float RESCALE_THRESHOLD = TB200_RESCALE_THRESHOLD;
-// The exponential passes of the two query tiles take turns (named barriers 1 and 2, see the
-// softmax loop): 1 = on.
-#ifndef TB200_FWD_ALTERNATE
-#define TB200_FWD_ALTERNATE 0
-#endif
-constexpr bool FWD_ALTERNATE = TB200_FWD_ALTERNATE != 0;
-#ifndef TB200_FWD_EXP_BATCH
-#define TB200_FWD_EXP_BATCH 1
-#endif
+constexpr float RESCALE_THRESHOLD = 8.f;
 
 struct FwdParams {
   AttnArgs a;
@@ -262,12 +250,7 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
     // CTA reads, are marked. Keeping K and V (2) cut the forward's DRAM reads of the masked
     // configuration by a quarter, but lines marked that way outlive the kernel and crowd out
     // whatever runs next (the backward's traffic doubled), so nothing is marked "kept".
-#ifndef TB200_FWD_L2_KV
-#define TB200_FWD_L2_KV 0
-#define TB200_FWD_L2_Q 1
-#define TB200_FWD_L2_MASK 0
-#endif
-    const uint64_t keep = ptx::l2_policy(TB200_FWD_L2_KV), once = ptx::l2_policy(TB200_FWD_L2_Q);
+    const uint64_t keep = ptx::l2_policy(0), once = ptx::l2_policy(1);
     ptx::mbar_expect_tx(&q_full[0], TILE_BYTES);
 #pragma unroll
     for (int c = 0; c < NBOX; ++c)
@@ -313,7 +296,7 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
     //     fence.proxy.async, since the next access to the stage is this bulk copy (async proxy).
     //   mask_full -> softmax threads: completes when the copy's bytes have landed (complete_tx).
     if (p.mask_tma) {
-      const uint64_t once = ptx::l2_policy(TB200_FWD_L2_MASK);
+      const uint64_t once = ptx::l2_policy(0);
       for (int j = 0; j < nmax; ++j) {
         const int stg = j & 1;
         const uint32_t ph = (j >> 1) & 1;
@@ -488,24 +471,6 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
       mask_row = reinterpret_cast<const T*>(p.mask) + (long long)b * p.a.ms[0] + (long long)h * p.a.ms[1] +
                  row_g * p.a.ms[2];
     float m_used = -INFINITY, l = 0.f;
-    // Turn taking of the two softmax warpgroups. Both query tiles need the SM's exponential unit for
-    // about as long as the tensor pipe needs for their products; left alone the two tiles drift
-    // into phase, both in their exponentials and then both in their products, each at half
-    // speed. So the exponential pass of a tile starts only when the other tile's has ended: tile t
-    // waits on named barrier 1 + t (128 waiting threads + 128 arrivals of the other warpgroup)
-    // and the other tile arrives on it after its own pass. Tile 0 goes first (tile 1 arrives
-    // once up front). Only the first nmin = min(n0, n1) passes of either tile are paired, and
-    // every bar.sync has exactly one matching bar.arrive, also when waits were aborted (the
-    // loops always run their full trip counts).
-    const int nmin = n0 < n1 ? n0 : n1;
-    auto turn_wait = [&](int j) {
-      if (FWD_ALTERNATE && j < nmin) asm volatile("bar.sync %0, 256;" ::"r"(1 + t) : "memory");
-    };
-    auto turn_pass = [&](int j) {
-      // tile 0's pass j lets tile 1's pass j go; tile 1's pass j lets tile 0's pass j + 1 go
-      if (FWD_ALTERNATE && (t == 0 ? j < nmin : j + 1 < nmin)) asm volatile("bar.arrive %0, 256;" ::"r"(2 - t) : "memory");
-    };
-    if (FWD_ALTERNATE && t == 1 && nmin > 0) asm volatile("bar.arrive 1, 256;" ::: "memory");
     for (int j = 0; j < n; ++j) {
       const long long kv0 = (long long)j * TK;
       // Mask values of this row and key tile. Staged tiles (D = 64) are read from shared memory
@@ -696,7 +661,6 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
         const uint64_t scale2 = am::pack2f(to_log2, to_log2);
         const uint64_t negm2 = am::pack2f(-m_safe, -m_safe);
         uint64_t lsum = am::pack2f(0.f, 0.f);
-#if TB200_FWD_EXP_BATCH
         // The exponentials of a block of 32 columns are written as three passes over the block
         // (arguments, exponentials, sums and packing) so that the 32 independent exp2 of a thread
         // are issued back to back instead of each one being followed by its dependants.
@@ -718,22 +682,6 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
           }
           ptx::tmem_st16(p_addr + c * 16, packed);
         };
-#else
-        const uint64_t lsum_b = am::pack2f(0.f, 0.f);
-        auto exp32 = [&](const uint32_t (&r)[32], int c) {
-          uint32_t packed[16];
-#pragma unroll
-          for (int i = 0; i < 32; i += 2) {
-            const uint64_t xx = am::fma2(am::pack2u(r[i], r[i + 1]), scale2, negm2);
-            float x0, x1;
-            am::unpack2f(xx, x0, x1);
-            const float p0 = am::ex2(x0), p1 = am::ex2(x1);
-            lsum = am::add2(lsum, am::pack2f(p0, p1));
-            packed[i >> 1] = am::cvt_pair<T>(p0, p1);
-          }
-          ptx::tmem_st16(p_addr + c * 16, packed);
-        };
-#endif
         if constexpr (P_SPLIT) {
           // P(j) goes over P(j-1): the product that read it must have completed (it has, as a rule:
           // it was issued a whole pass ago)
@@ -742,12 +690,10 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
             ptx::tc_fence_after();
           }
         }
-        turn_wait(j);
         exp32(sr[0], 0);
         exp32(sr[1], 1);
         exp32(sr[2], 2);
         exp32(sr[3], 3);
-        turn_pass(j);
         float l0, l1;
         am::unpack2f(am::add2(lsum, lsum_b), l0, l1);
         l += l0 + l1;

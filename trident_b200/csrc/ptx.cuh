@@ -112,19 +112,15 @@ __device__ inline uint64_t l2_policy_evict_first() {
   asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
   return p;
 }
-__device__ inline uint64_t l2_policy_evict_last() {
-  uint64_t p;
-  asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
-  return p;
-}
 __device__ inline uint64_t l2_policy_evict_normal() {
   uint64_t p;
   asm volatile("createpolicy.fractional.L2::evict_normal.b64 %0, 1.0;" : "=l"(p));
   return p;
 }
-// 0 = normal, 1 = first to go, 2 = kept
+// 0 = normal, 1 = first to go. (A "kept" priority is not offered: lines marked so outlive the
+// kernel and crowd the next kernel's working set out of L2.)
 __device__ inline uint64_t l2_policy(int kind) {
-  return kind == 1 ? l2_policy_evict_first() : kind == 2 ? l2_policy_evict_last() : l2_policy_evict_normal();
+  return kind == 1 ? l2_policy_evict_first() : l2_policy_evict_normal();
 }
 __device__ inline void prefetch_tensormap(const CUtensorMap* map) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
