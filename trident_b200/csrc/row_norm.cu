@@ -896,8 +896,12 @@ __global__ void __launch_bounds__(512, MINB)
     uint4 x[CHUNKS], g[CHUNKS];
     float sa, sb;
   };
+  // Rows are taken last to first: when this kernel follows the forward pass directly, the rows
+  // the forward touched last are the ones still in L2 (measured: bf16 [8192, 4096] forward +
+  // backward 65.0 -> 63.7 us).
   auto request = [&](RowRegs& r, int64_t row) {
     if (row < rows) {
+      row = rows - 1 - row;
 #pragma unroll
       for (int c = 0; c < CHUNKS; ++c) {
         const int col = (c * TPR + tid) * VEC;
@@ -914,6 +918,7 @@ __global__ void __launch_bounds__(512, MINB)
     }
   };
   auto process = [&](const RowRegs& r, int64_t row) {
+    row = rows - 1 - row;
     const float sa = r.sa, sb = r.sb;
     if constexpr (!RMS) {
       // LayerNorm: sa = mean, sb = rstd; xh = (x - mean) * rstd.

@@ -170,7 +170,10 @@ __global__ void __launch_bounds__(CTA_ROW ? 512 : 256)
   RowThread<CTA_ROW> rt;
   pdl_wait();     // (programmatic dependent launch: nothing is read before the previous kernel is done)
   pdl_release();  // the next kernel of the stream may be scheduled
-  for (int64_t row = rt.first_row(); row < rows; row += rt.row_step()) {
+  // Rows are taken last to first: after a forward pass over the same rows, the probabilities it
+  // wrote last are the ones still in L2.
+  for (int64_t it = rt.first_row(); it < rows; it += rt.row_step()) {
+    const int64_t row = rows - 1 - it;
     float ys[CHUNKS][VEC], gs[CHUNKS][VEC];
     load_row<T, CHUNKS, CTA_ROW>(ys, y + row * row_stride, cols, rt);
     load_row<T, CHUNKS, CTA_ROW>(gs, dy + row * row_stride, cols, rt);
