@@ -215,7 +215,8 @@ int tb200_attention_fwd(void* out, float* lse, const void* q, const void* k, con
                         const int64_t* v_strides, const int64_t* out_strides,
                         const int64_t* mask_strides /*nullable iff mask is*/, int is_causal,
                         float softmax_scale, int dtype, void* stream);
-/* dq, dk, dv (and dmask when non-null: dense [B,H,S,S], same dtype) from dout.
+/* dq, dk, dv (and dmask when non-null: dense [B,H,S,S], same dtype; the gradient of the additive
+ * mask is dS, which the tensor-core kernel writes from the registers it computes it in) from dout.
  * Replaces Softmax.backward_delta as launched at trident/operation/attention.py:161 and
  * kernel.Attention.backward (trident/kernel/attention.py:167-339; launched at
  * trident/operation/attention.py:170). dq/dk/dv/dout are contiguous [B,H,S,D]; q, k, v,

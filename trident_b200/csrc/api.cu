@@ -331,7 +331,7 @@ extern "C" int tb200_attention_bwd(void* dq, void* dk, void* dv, void* dmask, co
   TB200_REQUIRE(workspace_bytes >= (size_t)B * H * S * sizeof(float), TB200_ERR_WORKSPACE,
                 "attention_bwd: workspace too small");
   cudaStream_t st = (cudaStream_t)stream;
-  if (!dmask && attn_tc_supported(a, dtype, q, k, v, out) && aligned16(dout) &&
+  if (attn_tc_supported(a, dtype, q, k, v, out) && aligned16(dout) &&
       aligned16(dq) && aligned16(dk) && aligned16(dv)) {
     const size_t row_bytes = attn_row_scratch_bytes(B, H, S);
     const size_t need = row_bytes + (size_t)B * H * S * D * sizeof(float);
@@ -340,7 +340,7 @@ extern "C" int tb200_attention_bwd(void* dq, void* dk, void* dv, void* dmask, co
                   "path needs", workspace_bytes, need);
     TB200_REQUIRE(aligned16(workspace), TB200_ERR_INVALID, "attention_bwd: workspace must be 16-byte aligned");
     float* dq_acc = (float*)((char*)workspace + row_bytes);
-    int rc = launch_attn_bwd_tc(dq, dk, dv, dout, q, k, v, out, lse, (float*)workspace, dq_acc, mask, a,
+    int rc = launch_attn_bwd_tc(dq, dk, dv, dmask, dout, q, k, v, out, lse, (float*)workspace, dq_acc, mask, a,
                                 dtype, st);
     if (rc == 0) note_kernel("attn_tcgen05", 3);
     return rc;

@@ -44,7 +44,7 @@ int launch_attn_fwd_tc(void* out, float* lse, const void* q, const void* k, cons
 namespace tb200 {
 // row_scratch: 2 * B*H*S floats (-delta and -lse*log2e, written by a first small kernel);
 // dq_acc: fp32 scratch of B*H*S*D elements.
-int launch_attn_bwd_tc(void* dq, void* dk, void* dv, const void* dout, const void* q, const void* k,
+int launch_attn_bwd_tc(void* dq, void* dk, void* dv, void* dmask, const void* dout, const void* q, const void* k,
                        const void* v, const void* out, const float* lse, float* row_scratch,
                        float* dq_acc, const void* mask, const AttnArgs& a, int dtype, cudaStream_t st);
 }  // namespace tb200

@@ -84,6 +84,7 @@ struct BwdParams {
   const float* nlse2;   // [B,H,S]  -lse * log2(e)
   const float* ndelta;  // [B,H,S]  -sum_d out*dout
   const void* mask;
+  void* dmask;          // null, or the dense [B,H,S,S] gradient of the additive mask (= dS)
   int mask_tma;         // the mask tile is staged in shared memory by bulk tensor copies
   int mask_has_b, mask_has_h;  // 0 when that mask dimension is broadcast
   int* status;
@@ -132,7 +133,9 @@ __device__ inline void unpack_pair<__half>(uint32_t v, float& lo, float& hi) {
   hi = f.y;
 }
 
-template <typename T, int D, bool CAUSAL, bool MASKED>
+// DMASK: the kernel also writes dS as the dense gradient of the additive mask (a variant of its
+// own: as a run-time branch in stage B it cost the masked kernel 8 %)
+template <typename T, int D, bool CAUSAL, bool MASKED, bool DMASK = false>
 __global__ void __launch_bounds__(bwd_threads_for(D, MASKED), 1)
     attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                        const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do,
@@ -483,6 +486,18 @@ __global__ void __launch_bounds__(bwd_threads_for(D, MASKED), 1)
                          d2, d3);
             dd[g * 2] = am::cvt_pair<T>(d0, d1);
             dd[g * 2 + 1] = am::cvt_pair<T>(d2, d3);
+            if constexpr (DMASK) {
+              // the additive mask enters the scores after the scale: its gradient is dS itself.
+              // (a warp's lanes are 32 adjacent keys of one query row: 64-byte segments)
+              {
+                T* dm = reinterpret_cast<T*>(p.dmask) +
+                        (((long long)b * p.a.H + h) * p.a.S + ((long long)it * 128 + c * 32 + g * 4)) * p.a.S + kv_g;
+                dm[0] = Traits<T>::from_f(d0);
+                dm[p.a.S] = Traits<T>::from_f(d1);
+                dm[2 * p.a.S] = Traits<T>::from_f(d2);
+                dm[3 * p.a.S] = Traits<T>::from_f(d3);
+              }
+            }
           }
 #pragma unroll
           for (int i = 0; i < 16; ++i) pp[lc * 16 + i] = dd[i];  // P^T is no longer needed
@@ -734,12 +749,13 @@ static bool make_dq_map(CUtensorMap* map, float* base, uint64_t rows, uint64_t D
   return true;
 }
 
-template <typename T, int D, bool CAUSAL, bool MASKED>
+template <typename T, int D, bool CAUSAL, bool MASKED, bool DMASK = false>
 static int launch_bwd(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& md,
                       const CUtensorMap& mdq, const CUtensorMap& mmask, const BwdParams& p, cudaStream_t st) {
   constexpr int SMEM = 6 * 128 * D * 2 + 128 * 128 * 2 + 2048 + 128 + ((MASKED && D == 64) ? 2 * 128 * 128 * 2 : 0) +
                        (D == 64 ? 128 * D * 4 : 0);
-  auto kern = attn_bwd_tc_kernel<T, D, CAUSAL, MASKED>;
+  static_assert(MASKED || !DMASK, "a mask gradient needs a mask");
+  auto kern = attn_bwd_tc_kernel<T, D, CAUSAL, MASKED, DMASK>;
   static std::atomic<unsigned long long> optin_done{0};
   const cudaError_t attr_err = smem_optin_per_device(optin_done, reinterpret_cast<const void*>(kern), SMEM);
   if (attr_err != cudaSuccess) {
@@ -778,7 +794,7 @@ static int launch_bwd(const CUtensorMap& mq, const CUtensorMap& mk, const CUtens
 // scratch: [ndelta | nlse2] (2 * B*H*S floats, 256-byte aligned) followed by the fp32 dq
 // accumulator (B*H*S*D floats). Launches: row kernel (which also clears the accumulator), main
 // kernel, dq conversion.
-int launch_attn_bwd_tc(void* dq, void* dk, void* dv, const void* dout, const void* q, const void* k,
+int launch_attn_bwd_tc(void* dq, void* dk, void* dv, void* dmask, const void* dout, const void* q, const void* k,
                        const void* v, const void* out, const float* lse, float* row_scratch, float* dq_acc,
                        const void* mask, const AttnArgs& a, int dtype, cudaStream_t st) {
   CUtensorMap mq, mk, mv, md, mdq;
@@ -816,6 +832,7 @@ int launch_attn_bwd_tc(void* dq, void* dk, void* dv, const void* dout, const voi
   p.nlse2 = nlse2;
   p.ndelta = ndelta;
   p.mask = mask;
+  p.dmask = mask ? dmask : nullptr;
   p.status = device_status_ptr();
   p.scale_log2 = a.scale * LOG2E;
   p.nq = (int)(a.S / 128);
@@ -828,6 +845,8 @@ int launch_attn_bwd_tc(void* dq, void* dk, void* dv, const void* dout, const voi
     if (rc) return rc;
     if (a.causal)
       rc = launch_bwd<T, D, true, false>(mq, mk, mv, md, mdq, mmask, p, st);
+    else if (mask && p.dmask)
+      rc = launch_bwd<T, D, false, true, true>(mq, mk, mv, md, mdq, mmask, p, st);
     else if (mask)
       rc = launch_bwd<T, D, false, true>(mq, mk, mv, md, mdq, mmask, p, st);
     else
