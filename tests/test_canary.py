@@ -115,6 +115,8 @@ def test_linear_and_geglu_odd_shapes(B, M, N, K, dt, device):
         (2, 1, 256, 128, torch.bfloat16, "mask"),
         (1, 3, 1024, 128, torch.bfloat16, "none"),
         (2, 2, 64, 32, torch.float32, "mask_grad"),
+        (2, 2, 256, 64, torch.bfloat16, "mask_grad"),   # dense mask gradient written by the tensor-core backward
+        (1, 2, 384, 128, torch.float16, "mask_grad"),
         (1, 1, 16, 16, torch.float32, "causal"),
     ],
 )
